@@ -295,6 +295,123 @@ def build_kv_append(dev, seed=6, tokens=sum(SEQ_LENS), hkv=HKV):
             "fp8_bytes": elems * 3.0 + tokens * 4, "nvfp4_bytes": elems * (2 + 0.5 + 1 / 16) + tokens * 4}
 
 
+def reference_sm100_stage(dev, lens, which="fp8", hq=HQ, hkv=HKV, topk=TOPK, iters=5, check=True):
+    """Times the reference's own SM100 kernels on this GPU, through its public API
+    (`fmha_sm100_plan(..., kv_block_num=K)` + `fmha_sm100(..., kv_block_indexes=...)`, which routes long-Q sparse
+    calls to the CuTe-DSL `sparse_atten_func`; NVFP4 through `sparse_atten_nvfp4_kv_func`, the way
+    benchmarks/bench_sparse_attention_ops.py of the reference does), next to this library on the SAME inputs:
+    BF16 Q, K/V ~ N(0,1) stored as e4m3 with unit scale (the reference's sparse entry takes no K/V scales) or
+    NVFP4, shuffled page table, one top-k page list per 128-query block from random scores among the causally
+    visible pages.  Needs the reference installed under baseline/_ref (git-ignored); timing is CUDA events with
+    an L2 flush before every iteration, median -- the method of the reference's bench_gpu_time."""
+    import msa_b200
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "fmha_sm100")):
+        return {"unavailable": "baseline/_ref/fmha_sm100 is not installed"}
+    os.environ.setdefault("TORCH_EXTENSIONS_DIR", os.path.join(ref_root, "torch_ext"))
+    os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0")
+    if ref_root not in sys.path:
+        sys.path.insert(0, ref_root)
+    t_import = time.perf_counter()
+    import fmha_sm100 as ref                      # the reference package, unmodified
+    from fmha_sm100 import sparse as ref_sparse   # CuTe-DSL stack (interface.py, build_k2q_csr)
+    t_import = time.perf_counter() - t_import
+
+    g = torch.Generator(device=dev).manual_seed(11)
+    T, n_pages, maxp = sum(lens), sum(L // PAGE for L in lens), max(lens) // PAGE
+    q = torch.randn(T, hq, D, device=dev, dtype=torch.bfloat16, generator=g)
+    kf = torch.randn(n_pages, hkv, PAGE, D, device=dev, dtype=torch.bfloat16, generator=g)
+    vf = torch.randn(n_pages, hkv, PAGE, D, device=dev, dtype=torch.bfloat16, generator=g)
+    table = torch.randperm(n_pages, device=dev, generator=g).int()
+    nblk = T // PAGE
+    sc = torch.rand(hkv, maxp, nblk, device=dev, generator=g)
+    blk_in_req = torch.cat([torch.arange(L // PAGE, device=dev) for L in lens])
+    sc.masked_fill_(torch.arange(maxp, device=dev)[None, :, None] > blk_in_req[None, None, :], -float("inf"))
+    idx = msa_b200.sparse_topk_select(sc, topk if topk in (16, 32, 64) else 16, num_valid_pages=maxp)[:, :, :topk]
+    idx = idx.repeat_interleave(PAGE, dim=0).contiguous()
+    qo = torch.tensor(lens, dtype=torch.int32)
+    flops = effective_flops(lens, hq, topk)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    res = {"lens": list(lens), "num_qo_heads": hq, "num_kv_heads": hkv, "topk": topk, "kv": which,
+           "import_s": round(t_import, 1)}
+    plan_o = msa_b200.fmha_sm100_plan(qo, qo, hq, num_kv_heads=hkv, page_size=PAGE, kv_block_num=topk,
+                                      sparse_kernel_mode="prefill", device=dev)
+    if which == "fp8":
+        k8, v8 = kf.to(torch.float8_e4m3fn), vf.to(torch.float8_e4m3fn)
+        del kf, vf
+        ours = lambda: msa_b200.fmha_sm100(q, k8, v8, plan_o, kv_indices=table, kv_block_indexes=idx)[0]  # noqa: E731
+        t0 = time.perf_counter()
+        plan_r = ref.fmha_sm100_plan(qo, qo, hq, qo_offset=torch.zeros_like(qo), page_size=PAGE, kv_block_num=topk,
+                                     num_kv_heads=hkv, use_fp8_kvcache=True)
+        out_r = torch.empty(T, hq, D, device=dev, dtype=torch.bfloat16)
+        theirs = lambda: ref.fmha_sm100(q, k8, v8, plan_info=plan_r, kv_indices=table, out=out_r,  # noqa: E731
+                                        kv_block_indexes=idx)[0]
+        # the attention kernels alone, CSR prebuilt, as benchmarks/bench_sparse_attention_ops.py times NVFP4
+        cu = torch.zeros(len(lens) + 1, dtype=torch.int32, device=dev)
+        cu[1:] = torch.cumsum(qo.to(dev), 0)
+        q2k = idx.permute(1, 0, 2).contiguous()
+        pt = torch.zeros(len(lens), maxp, dtype=torch.int32, device=dev)
+        o = 0
+        for b, L in enumerate(lens):
+            pt[b, :L // PAGE] = table[o:o + L // PAGE]
+            o += L // PAGE
+        csr = lambda: ref_sparse.build_k2q_csr(q2k, cu, cu, PAGE, total_k=T, max_seqlen_k=max(lens),  # noqa: E731
+                                               max_seqlen_q=max(lens), total_rows=n_pages, qhead_per_kv=hq // hkv,
+                                               return_schedule=True)
+        rp, qi, sched = csr()
+        kern = lambda: ref_sparse.sparse_atten_func(q, k8, v8, rp, qi, topk, cu_seqlens_q=cu, cu_seqlens_k=cu,  # noqa: E731
+                                                    max_seqlen_q=max(lens), max_seqlen_k=max(lens), blk_kv=PAGE,
+                                                    causal=True, page_table=pt, seqused_k=qo.to(dev), schedule=sched)
+    else:
+        kq, vq = msa_b200.quantize_kv_bf16_to_nvfp4_128x4(kf, vf)
+        del kf, vf
+        ours = lambda: msa_b200.sparse_prefill_nvfp4(q, kq, vq, plan_o, table, idx)  # noqa: E731
+        t0 = time.perf_counter()
+        cu = torch.zeros(len(lens) + 1, dtype=torch.int32, device=dev)
+        cu[1:] = torch.cumsum(qo.to(dev), 0)
+        q2k = idx.permute(1, 0, 2).contiguous()
+        pt = torch.zeros(len(lens), maxp, dtype=torch.int32, device=dev)
+        o = 0
+        for b, L in enumerate(lens):
+            pt[b, :L // PAGE] = table[o:o + L // PAGE]
+            o += L // PAGE
+        csr = lambda: ref_sparse.build_k2q_csr(q2k, cu, cu, PAGE, total_k=T, max_seqlen_k=max(lens),  # noqa: E731
+                                               max_seqlen_q=max(lens), total_rows=n_pages, qhead_per_kv=hq // hkv,
+                                               return_schedule=True)
+        rp, qi, sched = csr()
+        kern = lambda: ref_sparse.sparse_atten_nvfp4_kv_func(  # noqa: E731
+            q, kq.data, vq.data, kq.scale_128x4, vq.scale_128x4, kq.global_scale, vq.global_scale, rp, qi, topk,
+            cu_seqlens_q=cu, cu_seqlens_k=cu, max_seqlen_q=max(lens), max_seqlen_k=max(lens), blk_kv=PAGE,
+            causal=True, partial_dtype=torch.bfloat16, page_table=pt, seqused_k=qo.to(dev), schedule=sched)
+        theirs = None
+    out_k = kern()                                  # first call: CuTe-DSL JIT compile
+    torch.cuda.synchronize()
+    res["reference_first_call_s"] = round(time.perf_counter() - t0, 1)
+    mk, _ = time_fn(kern, iters, 2, flush=flush)
+    res["reference_kernels"] = {"ms": mk, "tflops_effective": flops / (mk * 1e-3) / 1e12,
+                                "what": "sparse_atten_func (KV-outer forward + combine), CSR and schedule prebuilt"
+                                if which == "fp8" else "sparse_atten_nvfp4_kv_func, CSR and schedule prebuilt"}
+    mc, _ = time_fn(csr, iters, 2, flush=flush)
+    res["reference_build_k2q_csr_ms"] = mc
+    if theirs is not None:
+        theirs()
+        torch.cuda.synchronize()
+        ma, _ = time_fn(theirs, iters, 2, flush=flush)
+        res["reference_api"] = {"ms": ma, "tflops_effective": flops / (ma * 1e-3) / 1e12,
+                                "what": "fmha_sm100(..., kv_block_indexes=...) as its benchmark times it: page table "
+                                        "rebuild + build_k2q_csr + forward + combine per call"}
+    mo, _ = time_fn(ours, iters, 2, flush=flush)
+    res["ours"] = {"ms": mo, "tflops_effective": flops / (mo * 1e-3) / 1e12}
+    res["speedup_vs_reference_kernels"] = mk / mo
+    if check:
+        out_o = ours()
+        torch.cuda.synchronize()
+        diff = (out_o.float() - out_k.float()).abs()
+        res["max_abs_ours_vs_reference"] = float(diff.max())
+        res["mean_abs_ours_vs_reference"] = float(diff.mean())
+    return res
+
+
 def time_fn(fn, iters, warmup, flush=None):
     """Median and mean of per-call CUDA-event durations (ms) on the current stream."""
     for _ in range(warmup):
@@ -388,8 +505,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="skip stages / decode / e2e (profiling runs)")
-    ap.add_argument("--stage", default="prefill", choices=["prefill", "decode", "topk", "kvappend"],
+    ap.add_argument("--stage", default="prefill", choices=["prefill", "decode", "topk", "kvappend", "reference_sm100"],
                     help="profiling runs: time only this stage and print a short JSON line")
+    ap.add_argument("--ref-kv", default="both", choices=["both", "fp8", "nvfp4"],
+                    help="--stage reference_sm100: which K/V format to run")
     ap.add_argument("--decode-batch", type=int, default=32, help="requests of the decode case (131072-token contexts)")
     ap.add_argument("--lens", default="", help="comma-separated request lengths (multiples of 128) for a reduced "
                                                "profiling case; default = the benchmark batch")
@@ -436,6 +555,19 @@ def main():
         nbytes = ms_t.numel() * 4.0 + T * TOPK * 4
         print(json.dumps({"stage": "topk", "shape": list(ms_t.shape), "ms": mt, "gbs": nbytes / (mt * 1e-3) / 1e9,
                           "frac_of_hbm": nbytes / (mt * 1e-3) / 1e9 / peaks0["hbm_gbs"]}), flush=True)
+        return
+    if args.stage == "reference_sm100":
+        # the reference's SM100 kernels beside this library on the same inputs (1 GPU, CUDA events only)
+        out = {"stage": "reference_sm100"}
+        for which, kw in (("fp8", dict(lens=lens)),
+                          ("nvfp4", dict(lens=(32768,) * 8 if not args.lens else lens, hq=8, hkv=1, topk=32))):
+            if args.ref_kv not in ("both", which):
+                continue
+            try:
+                out[which] = reference_sm100_stage(dev, which=which, **kw)
+            except Exception as e:  # the reference failed to import, compile or launch on this box
+                out[which] = {"unavailable": f"{type(e).__name__}: {str(e).splitlines()[0] if str(e) else ''}"[:300]}
+        print(json.dumps(out), flush=True)
         return
     if args.stage == "kvappend":
         ka = build_kv_append(dev, tokens=sum(lens))

@@ -26,6 +26,16 @@ extern "C" {
 #define MSA_ERR_TIMEOUT (-3)     /* a bounded device-side wait ran out (status word) */
 #define MSA_ERR_DRIVER (-4)      /* driver entry point or tensor-map encode failed */
 #define MSA_ERR_TOO_LARGE (-5)   /* size beyond a stated maximum */
+/* msa_validate_inputs: the first rule of the index contract that the inputs break */
+#define MSA_EVAL_Q_ROWS (-101)            /* q rows != sum(qo_lens) */
+#define MSA_EVAL_KV_ROWS (-102)           /* ragged K/V rows != sum(kv_lens) */
+#define MSA_EVAL_PAGE_TABLE_LENGTH (-103) /* kv_indices length != sum(ceil(kv_lens / 128)) */
+#define MSA_EVAL_PAGE_TABLE_RANGE (-104)  /* a kv_indices entry outside [0, num_pages) */
+#define MSA_EVAL_LIST_SHAPE (-105)        /* kv_block_indexes heads not num_kv_heads | num_qo_heads, or topk <= 0 */
+#define MSA_EVAL_LIST_NEGATIVE (-106)     /* a page-list entry below -1 */
+#define MSA_EVAL_LIST_PADDING (-107)      /* a valid entry after a -1 (padding must be at the tail) */
+#define MSA_EVAL_LIST_RANGE (-108)        /* an entry >= the request's page count */
+#define MSA_EVAL_LIST_ORDER (-109)        /* entries not strictly ascending */
 
 /* K/V storage formats */
 #define MSA_KV_BF16 0
@@ -37,6 +47,55 @@ int msa_abi_version(void);
 
 /* Short text for a negative MSA_ERR_* code (host pointer, static storage). */
 const char* msa_error_string(int code);
+
+/* ---------------------------------------------------------------------------
+ * Planner (host only: every pointer below is a HOST pointer, nothing is launched).
+ * Replaces the TVM-FFI function `plan(...22 args...)` (python/fmha_sm100/csrc/fmha_sm100_plan.cu:18-35) and the
+ * Python planner around it (python/fmha_sm100/api.py:510-747): the persistent kernels here take 128-row query
+ * tiles round-robin from an ordered list, so the plan is that list (heaviest tile first), the page-table
+ * offsets of the requests and, for the decode kernels, each token's (request, last visible key) and the number
+ * of KV splits.  The caller copies the arrays it needs to the device and passes them as msa_fmha_args.work /
+ * msa_decode_args.{kv_page_indptr, token_request, token_pos, num_splits}.
+ */
+typedef struct msa_plan_desc {
+  int32_t batch;
+  const int32_t* qo_lens;   /* [batch] query tokens per request */
+  const int32_t* kv_lens;   /* [batch] keys per request */
+  const int32_t* qo_offset; /* [batch] causal offset (row i sees key j iff i + offset >= j); NULL = kv_len - qo_len */
+  int32_t causal;           /* 0: every key visible */
+  int32_t paged;            /* 1: work[6] counts page-table slots; 0: K/V tokens (ragged K/V) */
+  int32_t num_qo_heads, num_kv_heads;
+  int32_t kv_block_num;     /* page-list length of a sparse call (> 0), else <= 0 */
+  int32_t num_kv_splits;    /* > 0 forces the decode split count, else chosen for whole waves of CTAs */
+  int32_t num_sms;          /* SMs the decode split choice may assume (usable_SM_count), <= 0 = 148 */
+} msa_plan_desc;
+
+/* Sizes of the arrays msa_plan fills: query tiles, total query tokens, total page-table slots. */
+int msa_plan_sizes(const msa_plan_desc* desc, int32_t* n_work, int64_t* total_q, int64_t* total_pages);
+
+/* Fills (each may be NULL to skip it): work int32 [n_work, 8] (layout of msa_fmha_args.work),
+ * kv_page_indptr int32 [batch + 1], token_request / token_pos int32 [total_q], *num_splits. */
+int msa_plan(const msa_plan_desc* desc, int32_t* work, int32_t* kv_page_indptr, int32_t* token_request,
+             int32_t* token_pos, int32_t* num_splits);
+
+/* Host re-check of the index contract before a launch (host pointers; nothing is launched): what the asserts of
+ * `_validate_fmha_inputs` (python/fmha_sm100/api.py:128-263) check, on raw arrays.  Returns MSA_OK or the
+ * MSA_EVAL_* code of the first broken rule (rules in the order of the defines above); *where (may be NULL)
+ * receives the flat index of the first offending element of kv_indices / kv_block_indexes, else -1. */
+typedef struct msa_validate_args {
+  int32_t batch;
+  const int32_t* qo_lens;
+  const int32_t* kv_lens;
+  int64_t total_q;                 /* rows of q */
+  int64_t kv_rows;                 /* num_pages (paged) or rows of ragged K/V */
+  int32_t paged;
+  const int32_t* kv_indices;       /* [n_kv_indices] or NULL */
+  int64_t n_kv_indices;
+  const int32_t* kv_block_indexes; /* [total_q, list_heads, topk] or NULL */
+  int32_t list_heads, topk;
+  int32_t num_qo_heads, num_kv_heads;
+} msa_validate_args;
+int msa_validate_inputs(const msa_validate_args* args, int64_t* where);
 
 /* ---------------------------------------------------------------------------
  * Stage 2: top-k page selector.
@@ -81,7 +140,10 @@ typedef struct msa_fmha_args {
   const int32_t* work;    /* int32 [n_work, 8], one entry per 128-row query tile, heaviest first:
                              {request, first token (global), valid rows <= 128, first token (request-local),
                               kv_len, causal offset (row i sees key j iff i + offset >= j),
-                              first page-table slot of the request (paged) | first K/V token (ragged), 0} */
+                              first page-table slot of the request (paged) | first K/V token (ragged), 0}.
+                             With page lists (kv_block_indexes != NULL) kv_len is at most 16384 pages
+                             (2 097 152 keys); a longer request is skipped (zero output) and the status word
+                             receives MSA_ERR_UNSUPPORTED. */
   int32_t n_work;
   const int32_t* kv_indices;         /* flat physical page table (paged) */
   const int32_t* kv_block_indexes;   /* [total_q, list_heads, topk] request-local page ids, ascending, -1 tail;
@@ -98,13 +160,34 @@ typedef struct msa_fmha_args {
   float sm_scale;         /* softmax scale */
   float qk_scale;         /* q_scale * k_scale (* k global scale for nvfp4) */
   float v_scale;          /* v_scale * o_scale (* v global scale for nvfp4) */
-  int32_t* status;        /* device int32, zeroed by the caller; receives MSA_ERR_TIMEOUT if a wait ran out */
+  int32_t* status;        /* device int32, zeroed by the caller; receives MSA_ERR_TIMEOUT if a wait ran out,
+                             MSA_ERR_UNSUPPORTED for a request beyond the page-list limit above */
   int32_t max_ctas;       /* > 0 caps the persistent grid (the reference's usable_SM_count); 0 = one CTA per SM */
   int32_t qk_dim;         /* 0 or 128: all of the head dimension; 64: the score-only pass (out = NULL) uses only the
                              first 64 elements of q and k (a 64-wide proxy zero-padded to 128 costs half) */
+  int64_t max_score_tile_stride; /* elements between consecutive tiles of max_score; 0 = total_q (contiguous) */
+  int64_t max_score_head_stride; /* elements between consecutive heads; 0 = max_k_tiles * tile stride.  The two
+                                    strides let a call write its tokens into a slice [.., .., t0:t1] of a larger
+                                    score tensor (the decode and prefill halves of a mixed batch) */
 } msa_fmha_args;
 
 int msa_fmha_fwd(const msa_fmha_args* args, void* stream);
+
+/* k2q CSR -> per-query page lists, on the device.  The reference's sparse prefill is KV-outer and consumes the
+ * reverse index built by `build_k2q_csr` (python/fmha_sm100/cute/sparse_index_utils.py:331-420,
+ * python/fmha_sm100/cute/src/sm100/prepare_k2q_csr.py:54); the kernel here is query-stationary, so the
+ * CSR-driven entry points turn it back into kv_block_indexes before msa_fmha_fwd.
+ *   row_ptr     int32 [num_kv_heads, n_rows + 1] (row_ptr_stride elements between heads)
+ *   q_indices   int32 [num_kv_heads, >= nnz] request-local query ids (q_indices_stride between heads)
+ *   row_request / row_block  int32 [n_rows]: request and KV block of each CSR row (block-major packing)
+ *   cu_seqlens_q int32 [batch + 1]
+ *   counters    int32 [total_q * num_kv_heads] scratch (cleared by the call)
+ *   out         int32 [total_q, num_kv_heads, topk] ascending block ids, -1 tail; a query selected by more
+ *               than topk rows keeps topk of them.  topk in {4, 8, 16, 32, 64}. */
+int msa_k2q_csr_to_lists(const int32_t* row_ptr, const int32_t* q_indices, const int32_t* row_request,
+                         const int32_t* row_block, const int32_t* cu_seqlens_q, int32_t num_kv_heads,
+                         int32_t n_rows, int64_t row_ptr_stride, int64_t q_indices_stride, int64_t total_q,
+                         int32_t topk, int32_t* counters, int32_t* out, void* stream);
 
 /* ---------------------------------------------------------------------------
  * Stage 3 (decode): paged FP8 sparse decode, split-KV + combine.

@@ -3,8 +3,8 @@ hot path behind the reference's Python API names."""
 from .api import (PlanInfo, fmha_sm100, fmha_sm100_plan, plan_status, sparse_topk_select)  # noqa: F401
 from .quant import (Nvfp4QuantizedTensor, dequantize_nvfp4_128x4, quantize_bf16_to_nvfp4_128x4,  # noqa: F401
                     quantize_fp8_per_tensor, quantize_kv_bf16_to_nvfp4_128x4)
-from .sparse import (SparseDecodePagedAttentionWrapper, build_k2q_csr, k2q_csr_to_q2k, sparse_atten_func,  # noqa: F401
-                     sparse_atten_nvfp4_kv_func, sparse_prefill_nvfp4)
+from .sparse import (SparseDecodePagedAttentionWrapper, build_k2q_csr, k2q_csr_to_lists, k2q_csr_to_q2k,  # noqa: F401
+                     sparse_atten_func, sparse_atten_nvfp4_kv_func, sparse_decode_atten_func, sparse_prefill_nvfp4)
 from .host_pipeline import HostPrefillPipeline  # noqa: F401
 from .kv_cache import absmax_bf16, append_kv_fp8, append_kv_nvfp4  # noqa: F401
 from .shard import request_cost, scatter_rows, shard_batch, shard_requests  # noqa: F401

@@ -7,6 +7,7 @@ or fails to load, every entry point raises.
 from __future__ import annotations
 
 import ctypes
+import fcntl
 import os
 import subprocess
 import threading
@@ -16,10 +17,11 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 # MSA_B200_LIB points the loader at another build of the same ABI (e.g. one made with -DMSA_ROLE_TIMING)
 LIB_PATH = os.environ.get("MSA_B200_LIB") or os.path.join(_HERE, "libmsa_b200.so")
 CSRC = os.path.join(_HERE, "csrc")
-SOURCES = ["abi.cu", "topk.cu", "decode.cu", "fmha_host.cu", "kv_quant.cu"]
+SOURCES = ["abi.cu", "topk.cu", "decode.cu", "fmha_host.cu", "kv_quant.cu", "plan_host.cu", "csr.cu"]
 
 MSA_KV_BF16, MSA_KV_FP8_E4M3, MSA_KV_NVFP4 = 0, 1, 2
 MSA_ERR_TIMEOUT = -3
+ABI_VERSION = 2
 
 
 class MsaError(RuntimeError):
@@ -39,6 +41,7 @@ class FmhaArgs(Structure):
         ("kv_dtype", c_int32), ("paged", c_int32), ("causal", c_int32),
         ("sm_scale", c_float), ("qk_scale", c_float), ("v_scale", c_float),
         ("status", c_void_p), ("max_ctas", c_int32), ("qk_dim", c_int32),
+        ("max_score_tile_stride", c_int64), ("max_score_head_stride", c_int64),
     ]
 
 
@@ -65,23 +68,54 @@ class KvAppendArgs(Structure):
     ]
 
 
+class PlanDesc(Structure):
+    _fields_ = [
+        ("batch", c_int32), ("qo_lens", c_void_p), ("kv_lens", c_void_p), ("qo_offset", c_void_p),
+        ("causal", c_int32), ("paged", c_int32), ("num_qo_heads", c_int32), ("num_kv_heads", c_int32),
+        ("kv_block_num", c_int32), ("num_kv_splits", c_int32), ("num_sms", c_int32),
+    ]
+
+
+class ValidateArgs(Structure):
+    _fields_ = [
+        ("batch", c_int32), ("qo_lens", c_void_p), ("kv_lens", c_void_p),
+        ("total_q", c_int64), ("kv_rows", c_int64), ("paged", c_int32),
+        ("kv_indices", c_void_p), ("n_kv_indices", c_int64), ("kv_block_indexes", c_void_p),
+        ("list_heads", c_int32), ("topk", c_int32), ("num_qo_heads", c_int32), ("num_kv_heads", c_int32),
+    ]
+
+
 def _sources():
     return [s for s in SOURCES if os.path.exists(os.path.join(CSRC, s))]
 
 
-def build_library(verbose: bool = False) -> str:
+def build_library(verbose: bool = False, force: bool = True) -> str:
     """Compile every CUDA source for sm_100a into msa_b200/libmsa_b200.so."""
     nvcc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
-    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo",
-           "--shared", "-Xcompiler", "-fPIC", "-o", LIB_PATH] + _sources()
-    if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
-    r = subprocess.run(cmd, cwd=CSRC, capture_output=True, text=True)
-    if r.returncode != 0:
-        raise MsaError("nvcc failed:\n" + r.stdout + r.stderr)
-    if verbose:
-        print(r.stderr)
+    # Several processes may get here at once (one rank per GPU importing the package after a source edit):
+    # an exclusive file lock serialises them, and the library is written under a temporary name and renamed
+    # into place, so a process that is loading the old file never sees a half-written one.
+    with open(LIB_PATH + ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and not _needs_build():
+                return LIB_PATH          # another process built it while this one waited
+            tmp = f"{LIB_PATH}.{os.getpid()}.tmp"
+            cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo",
+                   "--shared", "-Xcompiler", "-fPIC", "-o", tmp] + _sources()
+            if verbose:
+                cmd.insert(1, "-Xptxas")
+                cmd.insert(2, "-v")
+            r = subprocess.run(cmd, cwd=CSRC, capture_output=True, text=True)
+            if r.returncode != 0:
+                if os.path.exists(tmp):
+                    os.remove(tmp)
+                raise MsaError("nvcc failed:\n" + r.stdout + r.stderr)
+            if verbose:
+                print(r.stderr)
+            os.replace(tmp, LIB_PATH)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
     return LIB_PATH
 
 
@@ -102,6 +136,15 @@ def _bind(lib):
     lib.msa_abi_version.restype = c_int32
     lib.msa_error_string.restype = c_char_p
     lib.msa_error_string.argtypes = [c_int32]
+    lib.msa_plan_sizes.restype = c_int32
+    lib.msa_plan_sizes.argtypes = [POINTER(PlanDesc), vp, vp, vp]
+    lib.msa_plan.restype = c_int32
+    lib.msa_plan.argtypes = [POINTER(PlanDesc), vp, vp, vp, vp, vp]
+    lib.msa_validate_inputs.restype = c_int32
+    lib.msa_validate_inputs.argtypes = [POINTER(ValidateArgs), vp]
+    lib.msa_k2q_csr_to_lists.restype = c_int32
+    lib.msa_k2q_csr_to_lists.argtypes = [vp, vp, vp, vp, vp, c_int32, c_int32, c_int64, c_int64, c_int64, c_int32,
+                                         vp, vp, vp]
     lib.msa_topk_select.restype = c_int32
     lib.msa_topk_select.argtypes = [vp, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, vp, vp]
     lib.msa_block_max.restype = c_int32
@@ -135,7 +178,7 @@ def get_lib():
             if not os.environ.get("MSA_B200_LIB") and _needs_build():
                 nvcc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
                 if os.path.exists(nvcc):
-                    build_library()
+                    build_library(force=False)
                 elif not os.path.exists(LIB_PATH):
                     raise MsaError(f"{LIB_PATH} is missing and nvcc is not available to build it")
             try:

@@ -53,28 +53,48 @@ class PlanInfo(dict):
     split-KV workspace of the decode path.  Reusable across layers."""
 
 
+def _np_i32(x) -> np.ndarray:
+    return np.ascontiguousarray(np.asarray(x, dtype=np.int32).reshape(-1))
+
+
+def _np_ptr(a: Optional[np.ndarray]):
+    return None if a is None else ctypes.c_void_p(a.ctypes.data)
+
+
+def _host_plan(qo_lens, kv_lens, qo_offset, causal: bool, paged: bool, num_qo_heads: int = 1, num_kv_heads: int = 1,
+               kv_block_num: int = -1, num_kv_splits: int = -1, num_sms: int = 0, decode: bool = False):
+    """Runs ``msa_plan`` (the host planner of libmsa_b200.so, standing in for
+    csrc/fmha_sm100_plan.cu:18-35 and csrc/include/plan.cuh:899-1054 of the reference) and
+    returns host arrays: ``(work[n_work, 8], kv_page_indptr[B + 1], token_request, token_pos, num_splits)``;
+    the token arrays are ``None`` unless ``decode``."""
+    lib = get_lib()
+    ql, kl = _np_i32(qo_lens), _np_i32(kv_lens)
+    off = None if qo_offset is None else _np_i32(qo_offset)
+    d = _lib.PlanDesc()
+    d.batch = int(ql.shape[0])
+    d.qo_lens, d.kv_lens, d.qo_offset = _np_ptr(ql), _np_ptr(kl), _np_ptr(off)
+    d.causal, d.paged = int(bool(causal)), int(bool(paged))
+    d.num_qo_heads, d.num_kv_heads = int(num_qo_heads), int(num_kv_heads)
+    d.kv_block_num, d.num_kv_splits, d.num_sms = int(kv_block_num), int(num_kv_splits or -1), int(num_sms)
+    n_work, total_q, total_pages = ctypes.c_int32(0), ctypes.c_int64(0), ctypes.c_int64(0)
+    check(lib.msa_plan_sizes(ctypes.byref(d), ctypes.byref(n_work), ctypes.byref(total_q), ctypes.byref(total_pages)),
+          "msa_plan_sizes")
+    work = np.zeros((n_work.value, 8), dtype=np.int32)
+    indptr = np.zeros(d.batch + 1, dtype=np.int32)
+    tok_req = np.zeros(total_q.value, dtype=np.int32) if decode else None
+    tok_pos = np.zeros(total_q.value, dtype=np.int32) if decode else None
+    splits = ctypes.c_int32(1)
+    check(lib.msa_plan(ctypes.byref(d), _np_ptr(work), _np_ptr(indptr), _np_ptr(tok_req), _np_ptr(tok_pos),
+                       ctypes.byref(splits)), "msa_plan")
+    return work, indptr, tok_req, tok_pos, int(splits.value)
+
+
 def build_work_list(qo_lens, kv_lens, qo_offset, causal: bool, paged: bool = True) -> np.ndarray:
     """One entry of 8 int32 per 128-row query tile: (request, first token (global),
     valid rows, first token (request-local), kv_len, causal offset, first page-table
-    slot | first K/V token of the request, 0), heaviest tiles first.  Takes the place
-    of the reference's GPU plan kernel (csrc/include/plan.cuh:899-1054): the
-    persistent CTAs take tiles round-robin from this list, so the only scheduling
-    decision left is the order."""
-    items = []
-    start = 0
-    kv_base = 0
-    for b, (ql, kl) in enumerate(zip(qo_lens, kv_lens)):
-        for t0 in range(0, ql, PAGE):
-            rows = min(PAGE, ql - t0)
-            vis = min(kl, t0 + rows + qo_offset[b]) if causal else kl
-            cost = max(0, (vis + PAGE - 1) // PAGE)
-            items.append((cost, b, start + t0, rows, t0, kl, qo_offset[b], kv_base, 0))
-        start += ql
-        kv_base += (kl + PAGE - 1) // PAGE if paged else kl
-    items.sort(key=lambda x: -x[0])
-    if not items:
-        return np.zeros((0, 8), dtype=np.int32)
-    return np.asarray([it[1:] for it in items], dtype=np.int32)
+    slot | first K/V token of the request, 0), heaviest tiles first -- the list the
+    persistent CTAs take tiles from round-robin.  Built by ``msa_plan``."""
+    return _host_plan(qo_lens, kv_lens, qo_offset, causal, paged)[0]
 
 
 def _fmha_sm100_plan(
@@ -123,8 +143,6 @@ def _fmha_sm100_plan(
 
     qo_offsets = np.concatenate([[0], np.cumsum(qo_lens)]).astype(np.int32)
     kv_offsets = np.concatenate([[0], np.cumsum(kv_lens)]).astype(np.int32)
-    pages = [(k + PAGE - 1) // PAGE for k in kv_lens]
-    indptr = np.concatenate([[0], np.cumsum(pages)]).astype(np.int32)
     max_qo_len = max(qo_lens) if qo_lens else 0
     total_q = int(qo_offsets[-1])
     # python/fmha_sm100/api.py:615-619
@@ -135,7 +153,12 @@ def _fmha_sm100_plan(
     sparse = kv_block_num > 0
     use_decode = sparse and (sparse_kernel_mode == "decode" or
                              (sparse_kernel_mode == "auto" and max_qo_len <= _prefill_qlen_threshold(True)))
-    work = build_work_list(qo_lens, kv_lens, off, causal, paged=page_size > 0)
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    if usable_SM_count > 0:
+        sms = min(sms, usable_SM_count)
+    work, indptr, tok_req, tok_pos, splits = _host_plan(
+        qo_lens, kv_lens, off, causal, page_size > 0, num_qo_heads, num_kv_heads, kv_block_num,
+        num_kv_splits if num_kv_splits is not None else -1, sms, decode=use_decode)
     plan = PlanInfo()
     plan["MM-SA-Nv"] = False
     plan["device"] = device
@@ -151,6 +174,7 @@ def _fmha_sm100_plan(
     plan["total_qo_len"] = total_q
     plan["qo_lens_host"] = qo_lens
     plan["kv_lens_host"] = kv_lens
+    plan["total_pages_host"] = int(indptr[-1])
     plan["qo_segment_lens"] = _i32(qo_lens, device)
     plan["kv_segment_lens"] = _i32(kv_lens, device)
     plan["qo_segment_offsets"] = torch.from_numpy(qo_offsets).to(device)
@@ -167,37 +191,8 @@ def _fmha_sm100_plan(
     plan["usable_SM_count"] = usable_SM_count
     if use_decode:
         # every token is its own row of the decode grid (python/fmha_sm100/api.py:398-429)
-        tok_req = np.repeat(np.arange(B, dtype=np.int32), qo_lens)
-        local = np.concatenate([np.arange(q, dtype=np.int32) for q in qo_lens]) if total_q else np.zeros(0, np.int32)
-        kvl = np.asarray(kv_lens, dtype=np.int64)[tok_req]
-        pos = np.minimum(local.astype(np.int64) + np.asarray(off, dtype=np.int64)[tok_req], kvl - 1)
-        if not causal:
-            pos = kvl - 1
         plan["token_request"] = torch.from_numpy(tok_req).to(device)
-        plan["token_pos"] = torch.from_numpy(pos.astype(np.int32)).to(device)
-        sms = torch.cuda.get_device_properties(device).multi_processor_count
-        if usable_SM_count > 0:
-            sms = min(sms, usable_SM_count)
-        hr = num_qo_heads // num_kv_heads
-        rows = max(1, total_q * num_kv_heads)
-        if num_kv_splits is not None and num_kv_splits > 0:
-            splits = min(num_kv_splits, kv_block_num)
-        else:
-            # aim for a whole number of waves: the GQA <= 8 kernel is persistent with one CTA per SM and every
-            # split costs a prologue and a merge; the GQA > 8 kernel keeps 2 CTAs per SM resident
-            resident = sms * (1 if hr <= 8 else 2)
-            splits = 1
-            best = None
-            for s in range(1, min(kv_block_num, 64) + 1):
-                if kv_block_num % s and s != kv_block_num:
-                    continue
-                ctas = rows * s
-                waves = math.ceil(ctas / resident)
-                eff = ctas / (waves * resident)
-                per = math.ceil(kv_block_num / s)
-                score = eff - 0.01 * s - (0.25 if per < 2 else 0.0)
-                if best is None or score > best:
-                    best, splits = score, s
+        plan["token_pos"] = torch.from_numpy(tok_pos).to(device)
         plan["num_kv_splits"] = int(splits)
         ws = get_lib().msa_decode_workspace_bytes(total_q, num_qo_heads, int(splits))
         plan["workspace"] = torch.empty(max(ws, 16), dtype=torch.uint8, device=device)
@@ -243,37 +238,40 @@ def fmha_sm100_plan(
 
 
 def _validate_fmha_inputs(q, k, v, plan, kv_indices, kv_block_indexes, is_paged):
-    """Host re-check of the index contract (python/fmha_sm100/api.py:128-263)."""
-    qo_lens, kv_lens = plan["qo_lens_host"], plan["kv_lens_host"]
+    """Host re-check of the index contract before a launch, by ``msa_validate_inputs`` of the library
+    (the rules of python/fmha_sm100/api.py:128-263); raises ``AssertionError`` naming the first broken
+    rule and the offending element, as the reference's asserts do.  Copies the index tensors to the host."""
     Hq, Hkv = plan["num_qo_heads"], plan["num_kv_heads"]
-    assert q.dim() == 3, f"q must be [total_qo_len, num_qo_heads, head_dim], got {q.shape}"
-    assert q.shape[0] == sum(qo_lens), f"sum(qo_segment_lens)={sum(qo_lens)} != q.shape[0]={q.shape[0]}"
-    assert q.shape[1] == Hq
+    if q.dim() != 3 or q.shape[1] != Hq:
+        raise AssertionError(f"q must be [total_qo_len, {Hq}, head_dim], got {tuple(q.shape)}")
     if is_paged:
-        assert k.dim() == 4, f"paged K must be [total_pages, H_kv, page_size, D], got {k.shape}"
-        assert k.shape[1] == Hkv and k.shape[2] == PAGE
-        if v is not None:
-            assert v.shape[0] == k.shape[0] and v.shape[1] == Hkv and v.shape[2] == PAGE
-        assert kv_indices is not None
-        kvi = kv_indices.cpu()
-        need = sum((x + PAGE - 1) // PAGE for x in kv_lens)
-        assert kvi.shape[0] == need, f"kv_indices length {kvi.shape[0]} != sum(ceil(kv_segment_lens/page_size))={need}"
-        assert (kvi >= 0).all() and (kvi < k.shape[0]).all(), "kv_indices has values outside the page pool"
-    else:
-        assert k.shape[0] == sum(kv_lens), f"sum(kv_segment_lens)={sum(kv_lens)} != k.shape[0]={k.shape[0]}"
+        if k.dim() != 4 or k.shape[1] != Hkv or k.shape[2] != PAGE:
+            raise AssertionError(f"paged K must be [total_pages, {Hkv}, {PAGE}, D], got {tuple(k.shape)}")
+        if v is not None and tuple(v.shape[:3]) != tuple(k.shape[:3]):
+            raise AssertionError(f"paged V {tuple(v.shape)} does not match K {tuple(k.shape)}")
+        if kv_indices is None:
+            raise AssertionError("paged K/V needs kv_indices")
+    ql, kl = _np_i32(plan["qo_lens_host"]), _np_i32(plan["kv_lens_host"])
+    kvi = None if kv_indices is None else _np_i32(kv_indices.detach().cpu().numpy())
+    bi = None
+    a = _lib.ValidateArgs()
     if kv_block_indexes is not None:
-        assert kv_block_indexes.dim() == 3 and kv_block_indexes.shape[0] == q.shape[0]
-        assert kv_block_indexes.shape[1] in (Hkv, Hq)
-        bi = kv_block_indexes.cpu()
-        valid = bi != -1
-        assert ((bi >= 0) | (bi == -1)).all(), "kv_block_indexes must contain only non-negative indices or -1"
-        assert (valid[:, :, :-1] >= valid[:, :, 1:]).all(), "kv_block_indexes: -1 padding must be at the end"
-        owner = torch.repeat_interleave(torch.arange(len(qo_lens)), torch.tensor(qo_lens))
-        npg = ((torch.tensor(kv_lens)[owner] + PAGE - 1) // PAGE).view(-1, 1, 1)
-        assert (bi[valid] < npg.expand_as(bi)[valid]).all(), "kv_block_indexes: index out of range for batch page count"
-        both = valid[:, :, :-1] & valid[:, :, 1:]
-        if both.any():
-            assert (bi[:, :, 1:][both] > bi[:, :, :-1][both]).all(), "kv_block_indexes: must be strictly ascending"
+        if kv_block_indexes.dim() != 3 or kv_block_indexes.shape[0] != q.shape[0]:
+            raise AssertionError(f"kv_block_indexes must be [total_q, heads, topk], got {tuple(kv_block_indexes.shape)}")
+        bi = _np_i32(kv_block_indexes.detach().cpu().numpy())
+        a.list_heads, a.topk = int(kv_block_indexes.shape[1]), int(kv_block_indexes.shape[2])
+    a.batch = int(ql.shape[0])
+    a.qo_lens, a.kv_lens = _np_ptr(ql), _np_ptr(kl)
+    a.total_q, a.kv_rows, a.paged = int(q.shape[0]), int(k.shape[0]), int(bool(is_paged))
+    a.kv_indices, a.n_kv_indices = _np_ptr(kvi), 0 if kvi is None else int(kvi.shape[0])
+    a.kv_block_indexes = _np_ptr(bi)
+    a.num_qo_heads, a.num_kv_heads = int(Hq), int(Hkv)
+    where = ctypes.c_int64(-1)
+    lib = get_lib()
+    rc = lib.msa_validate_inputs(ctypes.byref(a), ctypes.byref(where))
+    if rc != 0:
+        at = f" (flat element {where.value})" if where.value >= 0 else ""
+        raise AssertionError(f"{lib.msa_error_string(rc).decode()}{at}")
 
 
 def _kv_dtype_code(k: torch.Tensor) -> int:
@@ -309,6 +307,11 @@ def _run_prefill(q, k, v, plan, kv_indices, kv_block_indexes, qo_offset_t, out, 
     a.topk = kv_block_indexes.shape[2] if kv_block_indexes is not None else 0
     a.list_heads = kv_block_indexes.shape[1] if kv_block_indexes is not None else 0
     a.max_k_tiles = max_score.shape[1] if max_score is not None else 0
+    if max_score is not None:
+        # a slice [.., .., t0:t1] of a larger score tensor is written in place through its strides
+        if max_score.stride(2) != 1:
+            raise MsaError("max_score must be contiguous along the token dimension")
+        a.max_score_tile_stride, a.max_score_head_stride = int(max_score.stride(1)), int(max_score.stride(0))
     a.kv_dtype = kv_dtype
     a.paged = 1 if is_paged else 0
     a.causal = 1 if plan["causal"] else 0
@@ -476,50 +479,46 @@ def fmha_sm100(
     if not has_mixed:
         return _fmha_sm100(q, k, v, decode, out=out, max_score=max_score, kv_indices=kv_indices,
                            kv_block_indexes=kv_block_indexes, q_offset_override=q_offset_override, **kwargs)
-    decode_nnz = decode["total_qo_len"]
-    is_paged = kv_indices is not None
-    nnz_qo, num_qo_heads = q.shape[0], q.shape[1]
-    q_d, q_p = q[:decode_nnz], q[decode_nnz:]
-    if is_paged:
-        k_d = k_p = k
-        v_d = v_p = v
-        page_split = int(decode["kv_page_indptr"][-1].item())
-        idx_d, idx_p = kv_indices[:page_split], kv_indices[page_split:]
-    else:
-        kv_split = int(decode["kv_segment_offsets"][-1].item())
-        k_d, k_p = k[:kv_split], k[kv_split:]
-        v_d, v_p = v[:kv_split], v[kv_split:]
-        idx_d = idx_p = None
-    blk_d = kv_block_indexes[:decode_nnz] if kv_block_indexes is not None else None
-    blk_p = kv_block_indexes[decode_nnz:] if kv_block_indexes is not None else None
-    if isinstance(q_offset_override, int):
-        off_d = off_p = q_offset_override
-    elif q_offset_override is not None:
-        off_d, off_p = q_offset_override[:split], q_offset_override[split:]
-    else:
-        off_d = off_p = None
-    want_lse = bool(kwargs.get("return_lse", False))
-    r_d = _fmha_sm100(q_d, k_d, v_d, decode, kv_indices=idx_d, kv_block_indexes=blk_d, q_offset_override=off_d,
-                      **kwargs)
-    r_p = _fmha_sm100(q_p, k_p, v_p, prefill, kv_indices=idx_p, kv_block_indexes=blk_p, q_offset_override=off_p,
-                      **kwargs)
-    o_d, ms_d, o_p, ms_p = r_d[0], r_d[1], r_p[0], r_p[1]
-    combined_out = torch.cat([o_d, o_p], dim=0) if (o_d is not None and o_p is not None) else None
-    if out is not None and combined_out is not None:
-        out.copy_(combined_out)
-    if ms_d is not None and ms_p is not None:
-        kt = max(ms_d.shape[1], ms_p.shape[1])
-        combined_ms = torch.full((num_qo_heads, kt, nnz_qo), -float("inf"), dtype=torch.float32, device=q.device)
-        combined_ms[:, :ms_d.shape[1], :decode_nnz] = ms_d
-        combined_ms[:, :ms_p.shape[1], decode_nnz:] = ms_p
-    else:
-        combined_ms = ms_d if ms_d is not None else ms_p
-    if max_score is not None and combined_ms is not None:
-        max_score.copy_(combined_ms)
-    res = (out if out is not None else combined_out, max_score if max_score is not None else combined_ms)
-    if want_lse:
-        res = res + (torch.cat([r_d[2], r_p[2]], dim=0),)
-    return res
+    # Mixed batch: the leading short requests take the decode sub-plan, the rest the prefill sub-plan, and both
+    # write straight into their token ranges of one output / one score tensor (no concatenation afterwards).
+    n_dec, nnz, Hq = decode["total_qo_len"], q.shape[0], q.shape[1]
+    paged = kv_indices is not None
+    want_o = bool(kwargs.get("output_o", True)) or kv_block_indexes is not None
+    want_ms = bool(kwargs.get("output_maxscore", True)) and kv_block_indexes is None
+    tiles = [pl["max_k_tiles"] for pl in (decode, prefill)]
+    if min(tiles) == -1:
+        want_ms = False
+    if not want_ms:
+        want_o = True
+    if want_o and out is None:
+        out = torch.empty(nnz, Hq, HEAD_DIM, device=q.device, dtype=torch.bfloat16)
+    if want_ms and max_score is None:
+        max_score = torch.full((Hq, max(tiles), nnz), -float("inf"), dtype=torch.float32, device=q.device)
+    lses = []
+    for part, pl, tok in ((0, decode, slice(0, n_dec)), (1, prefill, slice(n_dec, nnz))):
+        req = slice(0, split) if part == 0 else slice(split, batch_size)
+        if paged:
+            n_pg = decode["total_pages_host"]
+            pages = slice(0, n_pg) if part == 0 else slice(n_pg, None)
+            k_part, v_part, idx_part = k, v, kv_indices[pages]
+        else:
+            n_kv = sum(decode["kv_lens_host"])
+            rows = slice(0, n_kv) if part == 0 else slice(n_kv, None)
+            k_part, v_part, idx_part = k[rows], (v[rows] if v is not None else None), None
+        if isinstance(q_offset_override, torch.Tensor):
+            off_part = q_offset_override[req]
+        else:
+            off_part = q_offset_override
+        res = _fmha_sm100(q[tok], k_part, v_part, pl, kv_indices=idx_part,
+                          kv_block_indexes=None if kv_block_indexes is None else kv_block_indexes[tok],
+                          q_offset_override=off_part, out=out[tok] if want_o else None,
+                          max_score=max_score[:, :pl["max_k_tiles"], tok] if want_ms else None, **kwargs)
+        if len(res) > 2:
+            lses.append(res[2])
+    result = (out if want_o else None, max_score if want_ms else None)
+    if lses:
+        result = result + (torch.cat(lses, dim=0),)
+    return result
 
 
 def plan_status(plan_info) -> int:

@@ -3,7 +3,7 @@
 
 extern "C" {
 
-int msa_abi_version(void) { return 1; }
+int msa_abi_version(void) { return 2; }
 
 const char* msa_error_string(int code) {
   switch (code) {
@@ -13,8 +13,37 @@ const char* msa_error_string(int code) {
     case MSA_ERR_TIMEOUT: return "device-side wait timed out";
     case MSA_ERR_DRIVER: return "CUDA driver entry point or tensor map encode failed";
     case MSA_ERR_TOO_LARGE: return "size beyond the supported maximum";
+    case MSA_EVAL_Q_ROWS: return "sum(qo_segment_lens) != q.shape[0]";
+    case MSA_EVAL_KV_ROWS: return "sum(kv_segment_lens) != k.shape[0]";
+    case MSA_EVAL_PAGE_TABLE_LENGTH: return "kv_indices length != sum(ceil(kv_segment_lens / page_size))";
+    case MSA_EVAL_PAGE_TABLE_RANGE: return "kv_indices has values outside the page pool";
+    case MSA_EVAL_LIST_SHAPE: return "kv_block_indexes must be [total_q, num_kv_heads | num_qo_heads, topk]";
+    case MSA_EVAL_LIST_NEGATIVE: return "kv_block_indexes must contain only non-negative indices or -1";
+    case MSA_EVAL_LIST_PADDING: return "kv_block_indexes: -1 padding must be at the end";
+    case MSA_EVAL_LIST_RANGE: return "kv_block_indexes: index out of range for batch page count";
+    case MSA_EVAL_LIST_ORDER: return "kv_block_indexes: must be strictly ascending";
     default: return code > 0 ? "CUDA runtime error" : "unknown error";
   }
+}
+
+int msa_plan_sizes(const msa_plan_desc* desc, int32_t* n_work, int64_t* total_q, int64_t* total_pages) {
+  return msa::plan_sizes(desc, n_work, total_q, total_pages);
+}
+
+int msa_plan(const msa_plan_desc* desc, int32_t* work, int32_t* kv_page_indptr, int32_t* token_request,
+             int32_t* token_pos, int32_t* num_splits) {
+  return msa::plan(desc, work, kv_page_indptr, token_request, token_pos, num_splits);
+}
+
+int msa_validate_inputs(const msa_validate_args* args, int64_t* where) { return msa::validate_inputs(args, where); }
+
+int msa_k2q_csr_to_lists(const int32_t* row_ptr, const int32_t* q_indices, const int32_t* row_request,
+                         const int32_t* row_block, const int32_t* cu_seqlens_q, int32_t num_kv_heads,
+                         int32_t n_rows, int64_t row_ptr_stride, int64_t q_indices_stride, int64_t total_q,
+                         int32_t topk, int32_t* counters, int32_t* out, void* stream) {
+  return msa::k2q_csr_to_lists(row_ptr, q_indices, row_request, row_block, cu_seqlens_q, num_kv_heads, n_rows,
+                               row_ptr_stride, q_indices_stride, total_q, topk, counters, out,
+                               static_cast<cudaStream_t>(stream));
 }
 
 int msa_topk_select(const float* max_score, int32_t num_heads, int32_t max_k_tiles, int32_t total_q, int32_t topk,

@@ -18,9 +18,11 @@
 //     (python/fmha_sm100/cute/test_sparse_atten.py:336-353).
 // Causal masking uses original key positions: key page*128+o is visible iff <= pos.
 //
-// Memory pipeline: every thread copies the sixteen 16-byte pieces it will consume itself with cp.async
-// into a private shared-memory slot, one page ahead of the page being computed, so a warp always has a
-// full 8 KiB slice in flight and no thread ever waits on another thread's copy.
+// Two memory pipelines.  GQA ratio <= 8 (decode_ring_kernel): persistent CTAs, a producer warp streams whole
+// pages through a shared-memory ring with TMA and eight consumer warps take alternate pages.  GQA ratio 9-16
+// (decode_kernel): every thread copies the sixteen 16-byte pieces it will consume itself with cp.async into a
+// private shared-memory slot, one page ahead of the page being computed, so a warp always has a full 8 KiB
+// slice in flight and no thread ever waits on another thread's copy.
 #include "common.cuh"
 #include "msa_internal.h"
 
@@ -367,9 +369,6 @@ constexpr int kRingStages = 5;
 // row, which makes the accumulator stores (a lane quad writes four rows at the same head-dims, 16 bytes each)
 // and the column-wise reads bank-conflict free.
 __device__ __forceinline__ int ring_red_index(int d, int row) { return (((d >> 2) ^ ((row >> 1) & 3)) << 2) | (d & 3); }
-#ifdef MSA_ROLE_TIMING
-#else
-#endif
 struct __align__(1024) DecodeRingSmem {
   uint8_t ring[kRingStages][2][16384];
   float red_o[8][8][128];       // chunk-swizzled: see ring_red_index
@@ -416,14 +415,16 @@ decode_ring_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
     tok = it / p.Hkv;
   };
 
-  // The list entries of one item, one per lane and round (a split holds at most 64 entries): logical page,
-  // or -1 when the entry is padding, out of range or entirely beyond the causal position; and its physical
-  // page.  Loaded with all lanes at once so that no index load sits in front of a page copy or a softmax step.
+  // The list entries of one item, 64 at a time (one per lane and round; a split of more than 64 entries is
+  // walked in several such chunks): logical page, or -1 when the entry is padding, out of range or entirely
+  // beyond the causal position; and its physical page.  Loaded with all lanes at once so that no index load
+  // sits in front of a page copy or a softmax step.
   struct ItemPages {
     int page[2], phys[2];
     int tok, g, split, pos;
   };
-  auto load_item_pages = [&](int it, bool want_phys) {
+  const int n_chunks = (p.entries_per_split + 63) >> 6;
+  auto load_item_pages = [&](int it, int chunk, bool want_phys) {
     ItemPages ip;
     item_coords(it, ip.tok, ip.g, ip.split);
     const int req = __ldg(p.tok_req + ip.tok);
@@ -434,7 +435,7 @@ decode_ring_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
     const int n_pages_req = __ldg(p.kv_page_indptr + req + 1) - page_base;
 #pragma unroll
     for (int rnd = 0; rnd < 2; ++rnd) {
-      const int e = e0 + rnd * 32 + lane;
+      const int e = e0 + chunk * 64 + rnd * 32 + lane;
       int pg = (e < e1) ? __ldg(list + e) : -1;
       if (pg >= n_pages_req || pg * 128 > ip.pos) pg = -1;
       ip.page[rnd] = pg;
@@ -454,11 +455,13 @@ decode_ring_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
     uint32_t seq = 0;
     bool ok = true;
     ItemPages nxt;
-    if (blockIdx.x < n_items) nxt = load_item_pages(blockIdx.x, true);
+    if (blockIdx.x < n_items) nxt = load_item_pages(blockIdx.x, 0, true);
     for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
-      const ItemPages cur = nxt;
-      if (it + gridDim.x < n_items) nxt = load_item_pages(it + gridDim.x, true);   // in flight while this item streams
+      ItemPages cur = nxt;
+      if (it + gridDim.x < n_items) nxt = load_item_pages(it + gridDim.x, 0, true);   // in flight while this item streams
       int n = 0;   // valid pages of the item so far: they go to the consumer groups alternately
+      for (int chunk = 0; chunk < n_chunks && ok; ++chunk) {
+      if (chunk > 0) cur = load_item_pages(it, chunk, true);
 #pragma unroll
       for (int rnd = 0; rnd < 2; ++rnd) {
         uint32_t mask = __ballot_sync(0xffffffffu, cur.page[rnd] >= 0);
@@ -480,6 +483,7 @@ decode_ring_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
           ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
           ++seq;
         }
+      }
       }
     }
     if (!ok && lane == 0) {
@@ -507,14 +511,14 @@ decode_ring_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
     ItemPages nxt_ip;
     uint2 nxt_q = make_uint2(0u, 0u);
     if (blockIdx.x < n_items) {
-      nxt_ip = load_item_pages(blockIdx.x, false);
+      nxt_ip = load_item_pages(blockIdx.x, 0, false);
       nxt_q = load_q_row(nxt_ip);
     }
     for (int it = blockIdx.x; it < n_items; it += gridDim.x) {
-      const ItemPages ip = nxt_ip;
+      ItemPages ip = nxt_ip;
       const uint2 raw = nxt_q;
       if (it + gridDim.x < n_items) {
-        nxt_ip = load_item_pages(it + gridDim.x, false);
+        nxt_ip = load_item_pages(it + gridDim.x, 0, false);
         nxt_q = load_q_row(nxt_ip);
       }
       const int tok = ip.tok, g = ip.g, split = ip.split, pos = ip.pos;
@@ -562,6 +566,8 @@ decode_ring_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
       float m0 = -INFINITY, l0 = 0.f;
 
       int n = 0;
+      for (int chunk = 0; chunk < n_chunks && ok; ++chunk) {
+      if (chunk > 0) ip = load_item_pages(it, chunk, false);
 #pragma unroll
       for (int rnd = 0; rnd < 2; ++rnd) {
        uint32_t mask = __ballot_sync(0xffffffffu, ip.page[rnd] >= 0);
@@ -674,6 +680,7 @@ decode_ring_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
         }
        }
       }
+      }
       // ---- merge the eight consumer warps --------------------------------------------
       l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
       l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -775,33 +782,26 @@ int decode_launch(const msa_decode_args* a, float* part_o, float* part_ml, cudaS
   const long long ctas = static_cast<long long>(p.T) * p.Hkv * p.nsplit;
   if (ctas > 0x7fffffffLL) return MSA_ERR_TOO_LARGE;
   constexpr int kDynSmem = 4 * 2 * 16 * 32 * 16;   // 64 KiB of copy slots (>= the 32 KiB merge buffer)
-  static bool configured = false;
-  if (!configured) {
+  constexpr int kRingSmem = static_cast<int>(sizeof(DecodeRingSmem)) + 1024;
+  static DeviceSetup setup;
+  int num_sms = 0;
+  const int src = setup.ensure(&num_sms, [] {
     cudaError_t e1 = cudaFuncSetAttribute(decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDynSmem);
-    cudaError_t e2 = cudaFuncSetAttribute(decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDynSmem);
     if (e1 != cudaSuccess) return static_cast<int>(e1);
-    if (e2 != cudaSuccess) return static_cast<int>(e2);
-    configured = true;
-  }
+    e1 = cudaFuncSetAttribute(decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDynSmem);
+    if (e1 != cudaSuccess) return static_cast<int>(e1);
+    e1 = cudaFuncSetAttribute(decode_ring_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingSmem);
+    if (e1 != cudaSuccess) return static_cast<int>(e1);
+    // the in-kernel register hand-over only balances if the CTA starts with exactly kRingRegsLaunch per thread
+    cudaFuncAttributes fa;
+    e1 = cudaFuncGetAttributes(&fa, decode_ring_kernel);
+    if (e1 != cudaSuccess) return static_cast<int>(e1);
+    if (fa.numRegs != kRingRegsLaunch) return static_cast<int>(MSA_ERR_UNSUPPORTED);
+    return static_cast<int>(MSA_OK);
+  });
+  if (src != MSA_OK) return src;
   if (p.hr <= 8 && a->num_pages > 0) {
     // persistent ring kernel: one CTA per SM over the (token, KV head, split) items
-    static int num_sms = 0;
-    static bool ring_configured = false;
-    constexpr int kRingSmem = static_cast<int>(sizeof(DecodeRingSmem)) + 1024;
-    if (!ring_configured) {
-      cudaError_t e1 = cudaFuncSetAttribute(decode_ring_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingSmem);
-      if (e1 != cudaSuccess) return static_cast<int>(e1);
-      int dev = 0;
-      e1 = cudaGetDevice(&dev);
-      if (e1 == cudaSuccess) e1 = cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-      if (e1 != cudaSuccess) return static_cast<int>(e1);
-      // the in-kernel register hand-over only balances if the CTA starts with exactly kRingRegsLaunch per thread
-      cudaFuncAttributes fa;
-      e1 = cudaFuncGetAttributes(&fa, decode_ring_kernel);
-      if (e1 != cudaSuccess) return static_cast<int>(e1);
-      if (fa.numRegs != kRingRegsLaunch) return MSA_ERR_UNSUPPORTED;
-      ring_configured = true;
-    }
     CUtensorMap mk, mv;
     int rc = make_paged_e4m3_map(&mk, a->k, a->num_pages, p.Hkv);
     if (rc == MSA_OK) rc = make_paged_e4m3_map(&mv, a->v, a->num_pages, p.Hkv);

@@ -74,17 +74,16 @@ int make_paged_e4m3_map(void* tensor_map, const void* kv, int64_t pages, int hkv
 }
 
 static long long* g_timing_buffer = nullptr;
-static int g_max_ctas = 0;  // 0 = one CTA per SM; set through msa_fmha_args.max_ctas (usable_SM_count)
 void set_timing_buffer(void* ptr) { g_timing_buffer = static_cast<long long*>(ptr); }
 
 template <int NT, int KVMODE>
 static int launch_fmha(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FmhaParams& p,
-                       cudaStream_t st) {
+                       int max_ctas, cudaStream_t st) {
   using Cfg = FmhaCfg<NT, KVMODE>;
-  static bool configured = false;
-  static int num_sms = 0;
+  static DeviceSetup setup;
+  int num_sms = 0;
   constexpr int smem = fmha_smem_bytes<NT, KVMODE>();
-  if (!configured) {
+  const int rc = setup.ensure(&num_sms, [] {
     cudaError_t e = cudaFuncSetAttribute(fmha_fwd_kernel<NT, KVMODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
     if (Cfg::kRebalance) {
@@ -92,17 +91,14 @@ static int launch_fmha(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
       cudaFuncAttributes fa;
       e = cudaFuncGetAttributes(&fa, fmha_fwd_kernel<NT, KVMODE>);
       if (e != cudaSuccess) return static_cast<int>(e);
-      if (fa.numRegs != Cfg::kRegsLaunch) return MSA_ERR_UNSUPPORTED;
+      if (fa.numRegs != Cfg::kRegsLaunch) return static_cast<int>(MSA_ERR_UNSUPPORTED);
     }
-    int dev = 0;
-    e = cudaGetDevice(&dev);
-    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
-  // persistent: one CTA per SM walks the item list with stride gridDim.x
+    return static_cast<int>(MSA_OK);
+  });
+  if (rc != MSA_OK) return rc;
+  // persistent: one CTA per SM walks the item list with stride gridDim.x; max_ctas > 0 caps the grid
   int ctas = p.n_items < num_sms ? p.n_items : num_sms;
-  if (g_max_ctas > 0 && g_max_ctas < ctas) ctas = g_max_ctas;
+  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   fmha_fwd_kernel<NT, KVMODE><<<static_cast<unsigned>(ctas), Cfg::kThreads, smem, st>>>(mq, mk, mv, p);
   return static_cast<int>(cudaGetLastError());
 }
@@ -123,6 +119,8 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
                  (a->list_heads != a->num_kv_heads && a->list_heads != a->num_qo_heads)))
     return MSA_ERR_INVALID;
   if (a->max_score != nullptr && a->max_k_tiles <= 0) return MSA_ERR_INVALID;
+  if (a->max_score_tile_stride < 0 || a->max_score_head_stride < 0) return MSA_ERR_INVALID;
+  if (a->max_score_tile_stride > 0 && a->max_score_tile_stride < a->total_q) return MSA_ERR_INVALID;
   if (a->qk_dim != 0 && a->qk_dim != 64 && a->qk_dim != 128) return MSA_ERR_INVALID;
   if (a->qk_dim == 64 && (a->out != nullptr || a->kv_dtype == MSA_KV_NVFP4)) return MSA_ERR_UNSUPPORTED;
   if (a->n_work <= 0 || a->total_q <= 0) return MSA_OK;
@@ -131,6 +129,8 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
   p.out = static_cast<__nv_bfloat16*>(a->out);
   p.lse = a->lse;
   p.max_score = a->max_score;
+  p.ms_tile = a->max_score_tile_stride > 0 ? a->max_score_tile_stride : a->total_q;
+  p.ms_head = a->max_score_head_stride > 0 ? a->max_score_head_stride : p.ms_tile * a->max_k_tiles;
   p.work = reinterpret_cast<const int4*>(a->work);
   p.kv_indices = a->kv_indices;
   p.kv_block_indexes = a->kv_block_indexes;
@@ -163,7 +163,6 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
   const long long n_items = static_cast<long long>(p.n_work) * p.n_head_groups;
   if (n_items > 0x7fffffffLL) return MSA_ERR_TOO_LARGE;
   p.n_items = static_cast<int>(n_items);
-  g_max_ctas = a->max_ctas;
 
   CUtensorMap mq, mk, mv;
   int rc = make_q_map(&mq, a->q, a->total_q, p.Hq);
@@ -179,12 +178,12 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
     if (rc != MSA_OK) return rc;
   }
   switch (a->kv_dtype * 2 + (nt - 1)) {
-    case 0: return launch_fmha<1, KV_BF16>(mq, mk, mv, p, st);
-    case 1: return launch_fmha<2, KV_BF16>(mq, mk, mv, p, st);
-    case 2: return launch_fmha<1, KV_FP8>(mq, mk, mv, p, st);
-    case 3: return launch_fmha<2, KV_FP8>(mq, mk, mv, p, st);
-    case 4: return launch_fmha<1, KV_NVFP4>(mq, mk, mv, p, st);
-    case 5: return launch_fmha<2, KV_NVFP4>(mq, mk, mv, p, st);
+    case 0: return launch_fmha<1, KV_BF16>(mq, mk, mv, p, a->max_ctas, st);
+    case 1: return launch_fmha<2, KV_BF16>(mq, mk, mv, p, a->max_ctas, st);
+    case 2: return launch_fmha<1, KV_FP8>(mq, mk, mv, p, a->max_ctas, st);
+    case 3: return launch_fmha<2, KV_FP8>(mq, mk, mv, p, a->max_ctas, st);
+    case 4: return launch_fmha<1, KV_NVFP4>(mq, mk, mv, p, a->max_ctas, st);
+    case 5: return launch_fmha<2, KV_NVFP4>(mq, mk, mv, p, a->max_ctas, st);
   }
   return MSA_ERR_UNSUPPORTED;
 }
@@ -302,9 +301,13 @@ int umma_selftest(const void* q, const void* k, const void* v, const void* pm, f
   if (rc == MSA_OK) rc = make_q_map(&mk, k, 128, 1);
   if (rc == MSA_OK) rc = make_q_map(&mv, v, 128, 1);
   if (rc != MSA_OK) return rc;
-  const int smem = static_cast<int>(sizeof(SelfTestSmem)) + 1024;
-  cudaError_t e = cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e != cudaSuccess) return static_cast<int>(e);
+  constexpr int smem = static_cast<int>(sizeof(SelfTestSmem)) + 1024;
+  static DeviceSetup setup;
+  rc = setup.ensure(nullptr, [] {
+    return static_cast<int>(
+        cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  });
+  if (rc != MSA_OK) return rc;
   umma_selftest_kernel<<<1, 128, smem, st>>>(mq, mk, mv, static_cast<const __nv_bfloat16*>(pm), s_out, o_out,
                                               status);
   return static_cast<int>(cudaGetLastError());

@@ -65,7 +65,8 @@ enum KvMode : int { KV_BF16 = 0, KV_FP8 = 1, KV_NVFP4 = 2 };
 struct FmhaParams {
   __nv_bfloat16* out;            // [total_q, Hq, 128] or null
   float* lse;                    // [total_q, Hq] natural-log LSE or null
-  float* max_score;              // [Hq, max_k_tiles, total_q] or null
+  float* max_score;              // [Hq, max_k_tiles, total_q] or null; element (h, tile, tok) at h * ms_head + tile * ms_tile + tok
+  long long ms_tile, ms_head;
   const int4* work;              // per query tile, two int4: {request, first token (global), valid rows, first token
                                  // (request-local)}, {kv_len, causal offset, first page-table slot | first K/V token, 0}
   const int* kv_indices;         // flat page table (paged)
@@ -179,6 +180,7 @@ struct PageWalk {
 // What every role needs to know about one work item.
 struct ItemInfo {
   int req, tok0, rows, qloc0, h0, g, kv_len, qo_off, kv_base, n_pages_req, walk_n;
+  bool oversize;
 };
 
 __device__ __forceinline__ ItemInfo load_item(const FmhaParams& p, int item, int nt) {
@@ -196,6 +198,10 @@ __device__ __forceinline__ ItemInfo load_item(const FmhaParams& p, int item, int
   it.kv_len = w2.x;
   it.qo_off = w2.y;
   it.kv_base = w2.z;
+  // the sparse pass keeps one bit per logical page of the request in shared memory: a longer request is not
+  // walked at all (every role sees an empty item, the producer reports MSA_ERR_UNSUPPORTED in the status word)
+  it.oversize = p.sparse && it.kv_len > kBitmapWords * 32 * 128;
+  if (it.oversize) it.kv_len = 0;
   it.n_pages_req = (it.kv_len + 127) >> 7;
   int kv_vis = it.kv_len;  // keys visible to the last row of the tile bound the dense walk
   if (p.causal) kv_vis = min(it.kv_len, it.qloc0 + it.rows + it.qo_off);
@@ -695,7 +701,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
         const float tmax = fmaxf(fmaxf(t0, t1), fmaxf(t2, t3));
         if (p.do_maxscore && row_valid)
-          __stwt(p.max_score + (static_cast<size_t>(h) * p.max_k_tiles + page) * p.total_q + tok, tmax * ms_scale);
+          __stwt(p.max_score + h * p.ms_head + page * p.ms_tile + tok, tmax * ms_scale);
 
         if (p.do_pv) {
           const float m_new = fmaxf(m_used, tmax);
@@ -787,6 +793,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       for (int item = item0; item < p.n_items && ok; item += item_step, ++j) {
         const ItemInfo info = load_item(p, item, NT);
         const int b = j & 1;
+        if (info.oversize && lane == 0) atomicExch(p.status, MSA_ERR_UNSUPPORTED);
         MSA_TBEGIN
         if (p.sparse) {
           // the buffer was used by item j - 2: wait until every walker released it

@@ -3,9 +3,44 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "../../include/msa_b200.h"
 
 namespace msa {
+
+// One-time set-up that belongs to a device, not to the process: function attributes
+// (cudaFuncSetAttribute applies to the current device only) and the SM count.  Keyed by the ordinal
+// of the device that is current at the call, so a process that drives several GPUs, or several host
+// threads on one GPU, gets each device configured exactly once.
+class DeviceSetup {
+ public:
+  static constexpr int kMaxDevices = 64;
+  // Runs configure() -> int (MSA_OK or an error code) the first time the current device is seen by this
+  // object and stores the device's SM count in *num_sms (if not null).
+  template <class F>
+  int ensure(int* num_sms, F&& configure) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev < 0 || dev >= kMaxDevices) return MSA_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> guard(mu_);
+    if (!done_[dev]) {
+      const int rc = configure();
+      if (rc != MSA_OK) return rc;
+      e = cudaDeviceGetAttribute(&sms_[dev], cudaDevAttrMultiProcessorCount, dev);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      done_[dev] = true;
+    }
+    if (num_sms != nullptr) *num_sms = sms_[dev];
+    return MSA_OK;
+  }
+
+ private:
+  std::mutex mu_;
+  bool done_[kMaxDevices] = {};
+  int sms_[kMaxDevices] = {};
+};
 
 int topk_select(const float* ms, int H, int K, int T, int topk, int nvp, int fb, int fe, int* out, cudaStream_t st);
 int block_max(const float* ms, int H, int K, int T, const int* block_starts, int n_blocks, float* out,
@@ -21,5 +56,12 @@ size_t decode_workspace_bytes(int n_tokens, int num_qo_heads, int num_splits);
 int decode_fwd_static(const msa_decode_args* a, cudaStream_t st);
 int kv_append(const msa_kv_append_args* a, cudaStream_t st);
 int absmax_bf16(const void* x, int64_t n, float* out, cudaStream_t st);
+int plan_sizes(const msa_plan_desc* d, int32_t* n_work, int64_t* total_q, int64_t* total_pages);
+int plan(const msa_plan_desc* d, int32_t* work, int32_t* kv_page_indptr, int32_t* token_request, int32_t* token_pos,
+         int32_t* num_splits);
+int validate_inputs(const msa_validate_args* a, int64_t* where);
+int k2q_csr_to_lists(const int* row_ptr, const int* q_indices, const int* row_request, const int* row_block,
+                     const int* cu_seqlens_q, int num_kv_heads, int n_rows, int64_t row_ptr_stride,
+                     int64_t q_indices_stride, int64_t total_q, int topk, int* counters, int* out, cudaStream_t st);
 
 }  // namespace msa

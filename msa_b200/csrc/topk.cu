@@ -387,14 +387,13 @@ __global__ void block_max_kernel(const float* __restrict__ ms, int K, int T, con
 template <int TOPK, int TOK>
 static int launch_topk_shape(const float* ms, int H, int K, int T, int nvp, int fb, int fe, int* out,
                              cudaStream_t st) {
-  static bool configured = false;
-  const int smem = kTopkChunk * (TOK + 1) * static_cast<int>(sizeof(float));
-  if (!configured) {
-    cudaError_t e =
-        cudaFuncSetAttribute(topk_select_kernel<TOPK, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  static DeviceSetup setup;
+  constexpr int smem = kTopkChunk * (TOK + 1) * static_cast<int>(sizeof(float));
+  const int rc = setup.ensure(nullptr, [] {
+    return static_cast<int>(
+        cudaFuncSetAttribute(topk_select_kernel<TOPK, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  });
+  if (rc != MSA_OK) return rc;
   dim3 grid((T + TOK - 1) / TOK, H);
   topk_select_kernel<TOPK, TOK><<<grid, TOK == 16 ? 256 : 128, smem, st>>>(ms, H, K, T, nvp, fb, fe, out);
   return static_cast<int>(cudaGetLastError());
@@ -404,13 +403,10 @@ template <int TOPK>
 static int launch_topk(const float* ms, int H, int K, int T, int nvp, int fb, int fe, int* out, cudaStream_t st) {
   // fewer wide CTAs than two per SM (decode-sized inputs): the narrow shape gives every row its own warp
   // and four times as many CTAs
-  static int num_sms = 0;
-  if (num_sms == 0) {
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-    if (e != cudaSuccess) return static_cast<int>(e);
-  }
+  static DeviceSetup setup;
+  int num_sms = 0;
+  const int rc = setup.ensure(&num_sms, [] { return static_cast<int>(MSA_OK); });
+  if (rc != MSA_OK) return rc;
   const long long wide_ctas = static_cast<long long>((T + 15) / 16) * H;
   if (wide_ctas < 2LL * num_sms) return launch_topk_shape<TOPK, 4>(ms, H, K, T, nvp, fb, fe, out, st);
   return launch_topk_shape<TOPK, 16>(ms, H, K, T, nvp, fb, fe, out, st);

@@ -15,11 +15,12 @@ from __future__ import annotations
 import math
 from typing import Optional
 
+import numpy as np
 import torch
 
 from . import _lib
 from ._lib import MsaError
-from .api import PAGE, _fmha_sm100_plan, _run_prefill, _run_decode
+from .api import PAGE, _fmha_sm100_plan, _ptr, _run_decode, _run_prefill, _stream
 from .quant import Nvfp4QuantizedTensor  # noqa: F401  (re-export for callers of the nvfp4 entry point)
 
 
@@ -114,45 +115,106 @@ def _flat_page_table(page_table: torch.Tensor, kv_lens, blk_kv: int) -> torch.Te
     return torch.cat(parts).to(torch.int32).contiguous()
 
 
+def _row_map_np(kv_caps, blk_kv):
+    """``_row_map`` on the host with numpy: (row_request, row_block) int32 arrays."""
+    nblk = np.asarray([(k + blk_kv - 1) // blk_kv for k in kv_caps], dtype=np.int64)
+    maxb = int(nblk.max()) if nblk.size else 0
+    blk, req = np.meshgrid(np.arange(maxb), np.arange(nblk.size), indexing="ij")
+    keep = blk < nblk[req]
+    return req[keep].astype(np.int32), blk[keep].astype(np.int32)
+
+
+def k2q_csr_to_lists(k2q_row_ptr: torch.Tensor, k2q_q_indices: torch.Tensor, topK: int, cu_seqlens_q: torch.Tensor,
+                     row_request: torch.Tensor, row_block: torch.Tensor, total_q: int) -> torch.Tensor:
+    """Device inverse of ``build_k2q_csr`` through ``msa_k2q_csr_to_lists``: int32
+    ``kv_block_indexes[total_q, Hkv, topK]`` (ascending request-local block ids, -1 tail).
+    ``row_request`` / ``row_block`` give the (request, block) of every CSR row (block-major packing)."""
+    lib = _lib.get_lib()
+    dev = k2q_row_ptr.device
+    Hkv = k2q_row_ptr.shape[0]
+    rp = k2q_row_ptr.to(torch.int32)
+    qi = k2q_q_indices.to(torch.int32)
+    if rp.stride(1) != 1:
+        rp = rp.contiguous()
+    if qi.stride(1) != 1:
+        qi = qi.contiguous()
+    out = torch.empty(total_q, Hkv, topK, dtype=torch.int32, device=dev)
+    counters = torch.empty(max(1, total_q * Hkv), dtype=torch.int32, device=dev)
+    cq = cu_seqlens_q.to(device=dev, dtype=torch.int32).contiguous()
+    _lib.check(lib.msa_k2q_csr_to_lists(_ptr(rp), _ptr(qi), _ptr(row_request), _ptr(row_block), _ptr(cq), Hkv,
+                                        int(row_request.numel()), rp.stride(0), qi.stride(0), total_q, topK,
+                                        _ptr(counters), _ptr(out), _stream()), "msa_k2q_csr_to_lists")
+    return out
+
+
+# Host metadata of recent CSR calls, keyed by the identity and version of the length tensors: a model calls
+# the attention once per layer with the same cu_seqlens / seqused_k tensors, and only the first call of a
+# step has to read them back to the host and plan.
+_CSR_PLAN_CACHE: "dict[tuple, dict]" = {}
+_CSR_PLAN_CACHE_MAX = 16
+
+
+def _tensor_key(t):
+    return None if t is None else (t.data_ptr(), t._version, tuple(t.shape), str(t.device))
+
+
+def _csr_plan(q, k, topK, cu_seqlens_q, cu_seqlens_k, blk_kv, causal, page_table, seqused_k):
+    Hq, Hkv = q.shape[1], k.shape[1]
+    key = (_tensor_key(cu_seqlens_q), _tensor_key(cu_seqlens_k), _tensor_key(seqused_k), _tensor_key(page_table),
+           Hq, Hkv, topK, bool(causal), str(q.device))
+    hit = _CSR_PLAN_CACHE.get(key)
+    if hit is not None:
+        return hit
+    cq = [int(x) for x in cu_seqlens_q.tolist()]
+    B = len(cq) - 1
+    qo_lens = [cq[i + 1] - cq[i] for i in range(B)]
+    paged = page_table is not None
+    ck = [int(x) for x in cu_seqlens_k.tolist()]
+    if seqused_k is not None:
+        kv_lens = [int(x) for x in seqused_k.tolist()]
+    elif paged:
+        kv_lens = [int(page_table.shape[1]) * blk_kv] * B
+    else:
+        kv_lens = [ck[i + 1] - ck[i] for i in range(B)]
+    # the CSR rows are laid out over the KV capacity the caller built it with
+    cap_csr = [ck[i + 1] - ck[i] for i in range(B)] if paged else kv_lens
+    rr, rb = _row_map_np(cap_csr, blk_kv)
+    plan = _fmha_sm100_plan(torch.tensor(qo_lens), torch.tensor(kv_lens), Hq, Hkv,
+                            qo_offset=None if causal else 0, page_size=PAGE if paged else -1,
+                            kv_block_num=topK, causal=causal, sparse_kernel_mode="prefill", device=q.device)
+    ent = {
+        "plan": plan,
+        "row_request": torch.from_numpy(rr).to(q.device),
+        "row_block": torch.from_numpy(rb).to(q.device),
+        "kv_indices": _flat_page_table(page_table, kv_lens, blk_kv) if paged else None,
+        "total_q": cq[-1],
+    }
+    if len(_CSR_PLAN_CACHE) >= _CSR_PLAN_CACHE_MAX:
+        _CSR_PLAN_CACHE.pop(next(iter(_CSR_PLAN_CACHE)))
+    _CSR_PLAN_CACHE[key] = ent
+    return ent
+
+
 def _csr_forward(q, k, v, k2q_row_ptr, k2q_q_indices, topK, cu_seqlens_q, cu_seqlens_k, blk_kv, causal,
                  softmax_scale, return_softmax_lse, page_table, seqused_k, kv_dtype, qk_scale, v_scale,
-                 k_sf=None, v_sf=None):
+                 k_sf=None, v_sf=None, usable_SM_count=-1):
     if blk_kv != PAGE:
         raise MsaError(f"blk_kv must be {PAGE}")
     if topK not in (4, 8, 16, 32, 64):
         raise ValueError(f"topK must be one of 4, 8, 16, 32, 64, got {topK}")
     if not q.is_cuda:
         raise MsaError("q must be a CUDA tensor: libmsa_b200 has no CPU path")
-    Hq, Hkv = q.shape[1], k.shape[1]
-    cq = [int(x) for x in cu_seqlens_q.tolist()]
-    B = len(cq) - 1
-    qo_lens = [cq[i + 1] - cq[i] for i in range(B)]
+    ent = _csr_plan(q, k, topK, cu_seqlens_q, cu_seqlens_k, blk_kv, causal, page_table, seqused_k)
+    plan = ent["plan"]
+    plan["usable_SM_count"] = usable_SM_count
     paged = page_table is not None
-    if seqused_k is not None:
-        kv_lens = [int(x) for x in seqused_k.tolist()]
-    elif paged:
-        kv_lens = [int(page_table.shape[1]) * blk_kv] * B
-    else:
-        ck = [int(x) for x in cu_seqlens_k.tolist()]
-        kv_lens = [ck[i + 1] - ck[i] for i in range(B)]
-    # the CSR rows are laid out over the KV capacity the caller built it with
-    if paged:
-        cap = [int(page_table.shape[1]) * blk_kv] * B
-        ckc = [int(x) for x in cu_seqlens_k.tolist()]
-        cap_csr = [ckc[i + 1] - ckc[i] for i in range(B)]
-    else:
-        cap_csr = kv_lens
-    q2k = k2q_csr_to_q2k(k2q_row_ptr, k2q_q_indices, topK, cu_seqlens_q, cap_csr, blk_kv)
-    plan = _fmha_sm100_plan(torch.tensor(qo_lens), torch.tensor(kv_lens), Hq, Hkv,
-                            qo_offset=None if causal else 0, page_size=PAGE if paged else -1,
-                            kv_block_num=topK, causal=causal, sparse_kernel_mode="prefill", device=q.device)
-    kv_indices = _flat_page_table(page_table, kv_lens, blk_kv) if paged else None
-    if not paged and any(c % blk_kv for c in cq[:0]):
-        raise MsaError("unreachable")
+    q2k = k2q_csr_to_lists(k2q_row_ptr, k2q_q_indices, topK, cu_seqlens_q, ent["row_request"], ent["row_block"],
+                           ent["total_q"])
+    Hq = q.shape[1]
     out = torch.empty(q.shape[0], Hq, 128, dtype=torch.bfloat16, device=q.device)
     lse = torch.empty(q.shape[0], Hq, dtype=torch.float32, device=q.device) if return_softmax_lse else None
     qq = q.to(torch.bfloat16).contiguous() if q.dtype != torch.bfloat16 else q.contiguous()
-    _run_prefill(qq, k.contiguous(), v.contiguous(), plan, kv_indices, q2k, plan["qo_offset"], out, None, lse,
+    _run_prefill(qq, k.contiguous(), v.contiguous(), plan, ent["kv_indices"], q2k, plan["qo_offset"], out, None, lse,
                  softmax_scale, qk_scale, v_scale, kv_dtype, paged, k_sf, v_sf)
     return (out, lse) if return_softmax_lse else out
 
@@ -179,7 +241,7 @@ def sparse_atten_func(q, k, v, k2q_row_ptr, k2q_q_indices, topK, *, cu_seqlens_q
     kv_dtype = _lib.MSA_KV_FP8_E4M3 if k.dtype == torch.float8_e4m3fn else _lib.MSA_KV_BF16
     return _csr_forward(q, k, v, k2q_row_ptr, k2q_q_indices, int(topK), cu_seqlens_q, cu_seqlens_k, int(blk_kv),
                         bool(causal), float(softmax_scale), bool(return_softmax_lse), page_table, seqused_k,
-                        kv_dtype, 1.0, 1.0)
+                        kv_dtype, 1.0, 1.0, usable_SM_count=int(usable_SM_count))
 
 
 def sparse_atten_nvfp4_kv_func(q, k, v, k_scale_128x4, v_scale_128x4, k_global_scale, v_global_scale, k2q_row_ptr,
@@ -222,46 +284,119 @@ def sparse_prefill_nvfp4(q, k_q, v_q, plan_info, kv_indices, kv_block_indexes, s
 
 
 class SparseDecodePagedAttentionWrapper:
-    """Paged FP8 decode with a plan/run split (python/fmha_sm100/cute/interface.py:1125-1423).
-    ``plan`` takes the page table and lengths once per batch shape; ``run`` attends
-    each request's new tokens to all of its pages (dense decode) or, when
-    ``kv_block_indexes`` is given, to the selected pages only."""
+    """Paged FP8 decode with a plan/run split; keyword signatures of
+    python/fmha_sm100/cute/interface.py:1125-1423.  ``plan`` takes the page table and
+    lengths once per batch shape; ``run`` attends each request's ``seqlen_q`` new tokens to
+    all of its pages (dense decode) or, when ``q2k_indices`` was planned, to the selected
+    pages only.  Differences from the reference: q may be bf16 as well as e4m3, any GQA ratio
+    up to 16 and any ``seqlen_q`` are accepted, and ``run`` also takes per-tensor
+    ``k_scale`` / ``v_scale`` and per-call ``kv_block_indexes`` ``[total_q, Hkv, topK]``.
+    ``enable_cuda_graph`` needs nothing here (``run`` launches a fixed sequence of kernels with
+    no host read-back); ``max_grid_size`` caps the SM count the split choice assumes,
+    ``fixed_split_size`` (pages per split) and ``disable_split_kv`` override it."""
 
     def __init__(self, *, blk_kv: int = 128, causal: bool = True):
-        if blk_kv != PAGE:
+        if int(blk_kv) != PAGE:
             raise MsaError(f"blk_kv must be {PAGE}")
-        self.blk_kv = blk_kv
-        self.causal = causal
+        self.blk_kv = int(blk_kv)
+        self.causal = bool(causal)
         self._plan = None
+        self._lists = None
+        self.batch = self.num_qo_heads = self.num_kv_heads = self.head_dim = None
+        self.page_table = self.seqused_k = self.q2k_indices = None
+        self.seqlen_q = self.max_seqlen_k = None
+        self.is_sparse = False
+        self.split_kv = False
 
-    def plan(self, page_table: torch.Tensor, seqused_k: torch.Tensor, *, num_qo_heads: int, num_kv_heads: int,
-             seqlen_q: int = 1, num_kv_splits: int = -1):
+    def plan(self, page_table: Optional[torch.Tensor] = None, seqused_k: Optional[torch.Tensor] = None, *,
+             seqlen_q: int = 1, max_seqlen_k: Optional[int] = None, q2k_indices: Optional[torch.Tensor] = None,
+             num_qo_heads: Optional[int] = None, num_kv_heads: Optional[int] = None, head_dim: Optional[int] = 128,
+             enable_cuda_graph: bool = False, max_grid_size: Optional[int] = None,
+             fixed_split_size: Optional[int] = None, disable_split_kv: bool = False, num_kv_splits: int = -1):
+        if page_table is None or seqused_k is None:
+            raise ValueError("decode plan requires page_table and seqused_k")
+        if page_table.ndim != 2:
+            raise ValueError("decode plan requires page_table with shape [B, max_num_pages_per_seq]")
+        if seqused_k.shape != (int(page_table.shape[0]),):
+            raise ValueError("decode plan requires seqused_k with shape [B]")
+        if not page_table.is_cuda:
+            raise ValueError("decode plan requires page_table and seqused_k to be CUDA tensors")
+        if num_qo_heads is None or num_kv_heads is None or head_dim is None:
+            raise ValueError("decode plan requires num_qo_heads, num_kv_heads, and head_dim")
+        if int(head_dim) != 128:
+            raise NotImplementedError("decode plan currently supports only head_dim=128")
+        if int(num_qo_heads) % int(num_kv_heads) != 0:
+            raise ValueError("decode plan requires num_qo_heads divisible by num_kv_heads")
+        if int(seqlen_q) <= 0:
+            raise ValueError("decode plan requires positive seqlen_q")
         kv_lens = [int(x) for x in seqused_k.tolist()]
         B = len(kv_lens)
+        if max_seqlen_k is not None and int(max_seqlen_k) < max(kv_lens + [0]):
+            raise ValueError(f"max_seqlen_k={max_seqlen_k} is below the longest request ({max(kv_lens)})")
+        dev = page_table.device
+        self.batch, self.num_qo_heads, self.num_kv_heads, self.head_dim = B, int(num_qo_heads), int(num_kv_heads), 128
+        self.page_table, self.seqused_k = page_table, seqused_k
+        self.seqlen_q, self.max_seqlen_k = int(seqlen_q), int(max_seqlen_k or max(kv_lens + [0]))
+        self.is_sparse = q2k_indices is not None
         self._kv_indices = _flat_page_table(page_table, kv_lens, self.blk_kv)
-        maxp = max((k + PAGE - 1) // PAGE for k in kv_lens)
-        self._plan = _fmha_sm100_plan(torch.tensor([seqlen_q] * B), torch.tensor(kv_lens), num_qo_heads, num_kv_heads,
-                                      page_size=PAGE, kv_block_num=maxp, causal=self.causal,
+        maxp = max([(k + PAGE - 1) // PAGE for k in kv_lens] + [1])
+        total_q = B * self.seqlen_q
+        if self.is_sparse:
+            if q2k_indices.dtype != torch.int32:
+                raise TypeError("decode plan requires q2k_indices to be torch.int32")
+            if q2k_indices.ndim != 3 or q2k_indices.shape[0] != self.num_kv_heads or q2k_indices.shape[1] != total_q:
+                raise ValueError("decode plan requires q2k_indices with shape [Hkv, total_q, topK]")
+            self.q2k_indices = q2k_indices
+            self._lists = q2k_indices.permute(1, 0, 2).contiguous()
+            list_len = int(q2k_indices.shape[2])
+        else:
+            dense = torch.arange(maxp, dtype=torch.int32, device=dev).view(1, 1, maxp)
+            npg = torch.tensor([(k + PAGE - 1) // PAGE for k in kv_lens], device=dev)
+            npg = torch.repeat_interleave(npg, self.seqlen_q).view(-1, 1, 1)
+            self._lists = torch.where(dense < npg, dense, torch.full_like(dense, -1)).expand(
+                total_q, self.num_kv_heads, maxp).contiguous()
+            list_len = maxp
+        if disable_split_kv:
+            num_kv_splits = 1
+        elif fixed_split_size is not None and int(fixed_split_size) > 0:
+            num_kv_splits = max(1, -(-list_len // int(fixed_split_size)))
+        self._plan = _fmha_sm100_plan(torch.tensor([self.seqlen_q] * B), torch.tensor(kv_lens), self.num_qo_heads,
+                                      self.num_kv_heads, page_size=PAGE, kv_block_num=list_len, causal=self.causal,
                                       sparse_kernel_mode="decode", num_kv_splits=num_kv_splits,
-                                      device=page_table.device)
-        dense = torch.arange(maxp, dtype=torch.int32, device=page_table.device).view(1, 1, maxp)
-        npg = torch.tensor([(k + PAGE - 1) // PAGE for k in kv_lens], device=page_table.device)
-        npg = torch.repeat_interleave(npg, seqlen_q).view(-1, 1, 1)
-        self._dense_lists = torch.where(dense < npg, dense, torch.full_like(dense, -1)).expand(
-            B * seqlen_q, num_kv_heads, maxp).contiguous()
+                                      usable_SM_count=-1 if max_grid_size is None else int(max_grid_size), device=dev)
+        self.split_kv = self._plan["num_kv_splits"] > 1
         return self
 
-    def run(self, q, k, v, *, softmax_scale: Optional[float] = None, k_scale: float = 1.0, v_scale: float = 1.0,
-            kv_block_indexes: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None):
+    def run(self, q, k, v, *, softmax_scale: Optional[float] = None, return_softmax_lse: bool = False,
+            out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None, k_scale: float = 1.0,
+            v_scale: float = 1.0, kv_block_indexes: Optional[torch.Tensor] = None):
         if self._plan is None:
-            raise MsaError("call plan() first")
-        if k.dtype != torch.float8_e4m3fn:
+            raise RuntimeError("decode wrapper must be planned before run")
+        if k.dtype != torch.float8_e4m3fn or v.dtype != torch.float8_e4m3fn:
             raise MsaError("the decode kernel takes e4m3 K/V")
+        if q.shape[0] != self.batch * self.seqlen_q or q.shape[1] != self.num_qo_heads:
+            raise ValueError(f"q must be [{self.batch * self.seqlen_q}, {self.num_qo_heads}, 128], got {tuple(q.shape)}")
         sm = q.shape[-1] ** -0.5 if softmax_scale is None else softmax_scale
         qq = q.to(torch.bfloat16).contiguous()
-        lists = self._dense_lists if kv_block_indexes is None else kv_block_indexes.to(torch.int32).contiguous()
+        lists = self._lists if kv_block_indexes is None else kv_block_indexes.to(torch.int32).contiguous()
         if out is None:
             out = torch.empty(qq.shape[0], qq.shape[1], 128, dtype=torch.bfloat16, device=q.device)
-        _run_decode(qq, k.contiguous(), v.contiguous(), self._plan, self._kv_indices, lists, out, None, sm, k_scale,
-                    v_scale)
-        return out
+        if return_softmax_lse and lse is None:
+            lse = torch.empty(qq.shape[0], qq.shape[1], dtype=torch.float32, device=q.device)
+        _run_decode(qq, k.contiguous(), v.contiguous(), self._plan, self._kv_indices, lists, out,
+                    lse if return_softmax_lse else None, sm, k_scale, v_scale)
+        return (out, lse) if return_softmax_lse else out
+
+
+def sparse_decode_atten_func(q, k, v, q2k_indices: Optional[torch.Tensor] = None, *, page_table: torch.Tensor,
+                             seqused_k: torch.Tensor, seqlen_q: int, max_seqlen_k: int, blk_kv: int = 128,
+                             causal: bool = True, softmax_scale: Optional[float] = None,
+                             return_softmax_lse: bool = False, schedule=None, O_partial=None, LSE_partial=None):
+    """One-shot paged FP8 decode (python/fmha_sm100/cute/interface.py:994-1122): plans and runs.
+    ``q2k_indices`` ``[Hkv, total_q, topK]`` selects pages, ``None`` attends to every page.
+    ``schedule`` / ``O_partial`` / ``LSE_partial`` belong to the reference's scheduler and are not needed:
+    the split-KV workspace is owned by the plan."""
+    w = SparseDecodePagedAttentionWrapper(blk_kv=blk_kv, causal=causal)
+    w.plan(page_table=page_table, seqused_k=seqused_k, seqlen_q=seqlen_q, max_seqlen_k=max_seqlen_k,
+           q2k_indices=q2k_indices, num_qo_heads=int(q.shape[1]), num_kv_heads=int(k.shape[1]), head_dim=int(q.shape[2]))
+    return w.run(q, k, v, softmax_scale=softmax_scale, return_softmax_lse=return_softmax_lse)

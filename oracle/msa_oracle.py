@@ -504,3 +504,22 @@ def pipeline_block_sparse(q, k_pages, v_pages, kv_indices, qo_lens, kv_lens, top
         idx[starts[i]:starts[i + 1]] = src.unsqueeze(0)
     out, lse = sparse_attention_paged(q, k_pages, v_pages, kv_indices, qo_lens, kv_lens, idx, sm_scale)
     return out, lse, idx, ms
+
+
+# ---------------------------------------------------------------------------
+# sub-sampled checks at full benchmark size
+# ---------------------------------------------------------------------------
+
+def sampled_sparse_error(out_rows, q_rows, k_pages, v_pages, table, kv_len, first_pos, idx_rows,
+                         k_scale: float = 1.0, v_scale: float = 1.0, token_chunk: int = 16) -> float:
+    """Max-abs difference between ``out_rows`` (``[n, Hq, D]``, any float dtype) and the oracle for ``n``
+    consecutive query tokens of ONE request: token ``i`` sits at request position ``first_pos + i`` of a
+    request with ``kv_len`` keys, ``table`` is that request's page table, ``idx_rows`` ``[n, Hkv, topk]`` its
+    page lists.  ``k_pages`` / ``v_pages`` are the page pool (or any tensor ``table`` indexes into).  Lets a
+    test compare a few (request, query block) slices of a benchmark-sized launch without running the oracle
+    on all of it."""
+    n = q_rows.shape[0]
+    ref, _ = sparse_attention_paged(q_rows, k_pages, v_pages, table, [n], [kv_len], idx_rows,
+                                    qo_offset=[first_pos], k_scale=k_scale, v_scale=v_scale,
+                                    token_chunk=token_chunk)
+    return float((out_rows.float() - ref).abs().max())

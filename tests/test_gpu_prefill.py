@@ -335,3 +335,101 @@ def test_properties_at_benchmark_scale():
     od, _ = msa_b200.fmha_sm100(q[:Ls], kp, vp, p_d, kv_indices=t1[:16], output_maxscore=False)
     os_, _ = msa_b200.fmha_sm100(q[:Ls], kp, vp, p_s, kv_indices=t1[:16], kv_block_indexes=full)
     assert torch.equal(od, os_)
+
+
+def _csr_inputs(qo, kv, idx):
+    """(cu_q, cu_k, page_table, seqused_k, row_ptr, q_indices) for per-token lists ``idx[total_q, Hkv, topk]``."""
+    cu_q = torch.tensor([0] + list(np.cumsum(qo)), dtype=torch.int32)
+    cu_k = torch.tensor([0] + list(np.cumsum(kv)), dtype=torch.int32)
+    rp, qi = msa_b200.build_k2q_csr(idx.permute(1, 0, 2).contiguous(), cu_q, cu_k, 128)
+    return cu_q, cu_k, rp, qi
+
+
+def test_sparse_atten_nvfp4_kv_func_entry_point():
+    """The reference-named NVFP4 entry point (python/fmha_sm100/cute/interface.py:768): CSR in, paged NVFP4
+    K/V; bit-identical to the page-list entry point and within the bf16 bound of the oracle on the dequantised
+    values."""
+    qo, kv, Hq, Hkv, topk = [256, 60], [1024, 700], 8, 2, 4
+    q, kp, vp, table, idx = _sparse_case(qo, kv, Hq, Hkv, topk, "bf16", "token", seed=35)
+    kq, vq = quant.quantize_kv_bf16_to_nvfp4_128x4(kp, vp)
+    cu_q, cu_k, rp, qi = _csr_inputs(qo, kv, idx)
+    ind = O.page_indptr(kv)
+    pt = torch.zeros(2, 8, dtype=torch.int32)
+    for b in range(2):
+        pt[b, :ind[b + 1] - ind[b]] = table[ind[b]:ind[b + 1]]
+    # the CSR rows are laid out over the page-table capacity (8 pages per request)
+    cu_k_cap = torch.tensor([0, 1024, 2048], dtype=torch.int32)
+    rp, qi = msa_b200.build_k2q_csr(idx.permute(1, 0, 2).contiguous(), cu_q, cu_k_cap, 128)
+    out, lse = msa_b200.sparse_atten_nvfp4_kv_func(
+        q.cuda(), kq.data.cuda(), vq.data.cuda(), kq.scale_128x4.cuda(), vq.scale_128x4.cuda(),
+        kq.global_scale.cuda(), vq.global_scale.cuda(), rp.cuda(), qi.cuda(), topk, cu_seqlens_q=cu_q.cuda(),
+        cu_seqlens_k=cu_k_cap.cuda(), max_seqlen_q=max(qo), max_seqlen_k=max(kv), blk_kv=128, causal=True,
+        return_softmax_lse=True, page_table=pt.cuda(), seqused_k=torch.tensor(kv, dtype=torch.int32).cuda())
+    plan = msa_b200.fmha_sm100_plan(torch.tensor(qo), torch.tensor(kv), Hq, num_kv_heads=Hkv, page_size=128,
+                                    kv_block_num=topk, sparse_kernel_mode="prefill")
+    dev = lambda t: quant.Nvfp4QuantizedTensor(t.data.cuda(), t.scale_128x4.cuda(), t.global_scale.cuda(),  # noqa: E731
+                                               t.logical_scale_shape, t.original_shape)
+    out2 = msa_b200.sparse_prefill_nvfp4(q.cuda(), dev(kq), dev(vq), plan, table.cuda(), idx.cuda())
+    assert torch.equal(out, out2)
+    kr, vr = quant.dequantize_nvfp4_128x4(kq), quant.dequantize_nvfp4_128x4(vq)
+    ref, lse_ref = O.sparse_attention_paged(q, kr, vr, table, qo, kv, idx)
+    assert (out.float().cpu() - ref).abs().max() <= TOL["bf16"]
+    fin = torch.isfinite(lse_ref)
+    assert torch.allclose(lse.cpu()[fin], lse_ref[fin], atol=2e-2, rtol=1e-3)
+
+
+def test_csr_to_lists_kernel_inverts_build_k2q_csr():
+    """msa_k2q_csr_to_lists on the device == the host inverse, for ragged requests with short and empty lists."""
+    g = torch.Generator().manual_seed(8)
+    qo, kv, Hkv, topk = [37, 0, 300], [1000, 128, 5000], 3, 8
+    T = sum(qo)
+    idx = torch.full((T, Hkv, topk), -1, dtype=torch.int32)
+    t = 0
+    for ql, kl in zip(qo, kv):
+        npg = (kl + 127) // 128
+        for i in range(ql):
+            for h in range(Hkv):
+                n = int(torch.randint(0, min(topk, npg) + 1, (1,), generator=g))
+                idx[t, h, :n] = torch.randperm(npg, generator=g)[:n].sort().values.int()
+            t += 1
+    cu_q, cu_k, rp, qi = _csr_inputs(qo, kv, idx)
+    from msa_b200.sparse import _row_map_np
+    rr, rb = _row_map_np(kv, 128)
+    got = msa_b200.k2q_csr_to_lists(rp.cuda(), qi.cuda(), topk, cu_q.cuda(), torch.from_numpy(rr).cuda(),
+                                    torch.from_numpy(rb).cuda(), T)
+    assert torch.equal(got.cpu(), idx)
+    assert torch.equal(msa_b200.k2q_csr_to_q2k(rp, qi, topk, cu_q, kv, 128), idx)
+
+
+def test_usable_sm_count_caps_the_grid_without_changing_results():
+    qo, kv, Hq, Hkv, topk = [700, 300], [2000, 1500], 8, 2, 8
+    q, kp, vp, table, idx = _sparse_case(qo, kv, Hq, Hkv, topk, "fp8", "token", seed=51)
+    kd, vd, _, _, kw = _quantise(kp, vp, "fp8")
+    outs = []
+    for sm in (-1, 16, 1):
+        plan = msa_b200.fmha_sm100_plan(torch.tensor(qo), torch.tensor(kv), Hq, num_kv_heads=Hkv, page_size=128,
+                                        kv_block_num=topk, sparse_kernel_mode="prefill", usable_SM_count=sm)
+        outs.append(msa_b200.fmha_sm100(q.cuda(), kd, vd, plan, kv_indices=table.cuda(), kv_block_indexes=idx.cuda(),
+                                        **kw)[0])
+        assert msa_b200.plan_status(plan) == 0
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+
+
+def test_mixed_batch_writes_straight_into_caller_buffers():
+    """Dense mixed batch (two short requests, one long): O and the max scores land in the caller's tensors,
+    decode and prefill halves side by side, and equal the two halves run separately."""
+    qo, kv = [1, 2, 300], [500, 900, 1000]
+    kp, vp, table = make_paged(kv, 2, 5)
+    q = torch.randn(sum(qo), 8, 128, generator=torch.Generator().manual_seed(6)).to(torch.bfloat16)
+    plan = msa_b200.fmha_sm100_plan(torch.tensor(qo), torch.tensor(kv), 8, num_kv_heads=2, page_size=128,
+                                    output_maxscore=True)
+    assert plan[0] and plan[1] == 2         # split at the first request longer than 128 query tokens
+    out_buf = torch.zeros(sum(qo), 8, 128, dtype=torch.bfloat16, device="cuda")
+    ms_buf = torch.full((8, 128, sum(qo)), -float("inf"), device="cuda")
+    out, ms = msa_b200.fmha_sm100(q.cuda(), kp.cuda(), vp.cuda(), plan, kv_indices=table.cuda(), out=out_buf,
+                                  max_score=ms_buf, output_maxscore=True)
+    assert out.data_ptr() == out_buf.data_ptr() and ms.data_ptr() == ms_buf.data_ptr()
+    ref, _ = O.dense_attention_paged(q, kp, vp, table, qo, kv)
+    assert (out.float().cpu() - ref).abs().max() <= TOL["bf16"]
+    msref = O.tile_max_score_paged(q, kp, table, qo, kv, 128)
+    assert torch.equal(torch.isfinite(ms.cpu()), torch.isfinite(msref))

@@ -25,13 +25,13 @@ def test_library_exports_every_declared_symbol():
     lib = msa_b200.get_lib()
     for n in sorted(names):
         assert hasattr(lib, n), f"{n} declared in the header but not exported"
-    assert lib.msa_abi_version() == 1
+    assert lib.msa_abi_version() == 2
     assert lib.msa_error_string(-3).decode().startswith("device-side wait")
 
 
 def test_struct_layout_matches_header_sizes():
     # pointers 8 B, int64 8 B, int32/float 4 B: the ctypes mirror must not be smaller than the C struct
-    assert ctypes.sizeof(_lib.FmhaArgs) % 8 == 0 and ctypes.sizeof(_lib.FmhaArgs) == 176
+    assert ctypes.sizeof(_lib.FmhaArgs) % 8 == 0 and ctypes.sizeof(_lib.FmhaArgs) == 192
     assert ctypes.sizeof(_lib.DecodeArgs) == 144
 
 
@@ -119,3 +119,138 @@ def test_header_is_plain_c(tmp_path):
                     str(src), "-o", str(exe)], check=True)
     out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
     assert int(out[0]) == ctypes.sizeof(_lib.FmhaArgs) and int(out[1]) == ctypes.sizeof(_lib.DecodeArgs)
+
+
+def _validate(qo, kv, total_q, kv_rows, paged, kvi, lists, Hq=4, Hkv=2):
+    a = _lib.ValidateArgs()
+    ql, kl = np.asarray(qo, np.int32), np.asarray(kv, np.int32)
+    a.batch, a.qo_lens, a.kv_lens = len(qo), ql.ctypes.data, kl.ctypes.data
+    a.total_q, a.kv_rows, a.paged = total_q, kv_rows, paged
+    keep = [ql, kl]
+    if kvi is not None:
+        kvi = np.ascontiguousarray(kvi, np.int32)
+        keep.append(kvi)
+        a.kv_indices, a.n_kv_indices = kvi.ctypes.data, kvi.size
+    if lists is not None:
+        lists = np.ascontiguousarray(lists, np.int32)
+        keep.append(lists)
+        a.kv_block_indexes, a.list_heads, a.topk = lists.ctypes.data, lists.shape[1], lists.shape[2]
+    a.num_qo_heads, a.num_kv_heads = Hq, Hkv
+    where = ctypes.c_int64(-7)
+    rc = msa_b200.get_lib().msa_validate_inputs(ctypes.byref(a), ctypes.byref(where))
+    return rc, where.value
+
+
+def test_validator_rejects_each_broken_rule_before_any_launch():
+    """msa_validate_inputs on host arrays: every rule of the index contract (reference api.py:128-263),
+    with the first offending element."""
+    qo, kv = [3, 2], [300, 129]                       # 3 + 2 pages
+    good = np.full((5, 2, 4), -1, np.int32)
+    good[:3, :, :3] = [0, 1, 2]
+    good[3:, :, :2] = [0, 1]
+    table = np.arange(5, dtype=np.int32)[::-1]
+    assert _validate(qo, kv, 5, 5, 1, table, good) == (0, -1)
+    assert _validate(qo, kv, 5, 5, 1, table, None) == (0, -1)
+    assert _validate(qo, kv, 6, 5, 1, table, good)[0] == -101                      # q rows
+    assert _validate(qo, kv, 5, 428, 0, None, good)[0] == -102                     # ragged K/V rows
+    assert _validate(qo, kv, 5, 429, 0, None, good)[0] == 0
+    assert _validate(qo, kv, 5, 5, 1, table[:4], good)[0] == -103                  # short kv_indices
+    bad_t = table.copy()
+    bad_t[3] = 5
+    assert _validate(qo, kv, 5, 5, 1, bad_t, good) == (-104, 3)                    # page outside the pool
+    bad_t[3] = -1
+    assert _validate(qo, kv, 5, 5, 1, bad_t, good) == (-104, 3)
+    assert _validate(qo, kv, 5, 5, 1, table, good[:, :1].repeat(3, 1))[0] == -105  # heads neither Hkv nor Hq
+    for value, at, code in ((-2, (1, 0, 1), -106),        # below -1
+                            (1, (4, 1, 3), -107),         # valid entry after the -1 tail started
+                            (3, (2, 1, 2), -108),         # >= the request's 3 pages
+                            (2, (3, 0, 1), -108),         # >= the second request's 2 pages
+                            (0, (0, 1, 1), -109)):        # not strictly ascending
+        bad = good.copy()
+        bad[at] = value
+        flat = (at[0] * 2 + at[1]) * 4 + at[2]
+        assert _validate(qo, kv, 5, 5, 1, table, bad) == (code, flat), (value, at)
+    # rule order: a -2 anywhere is reported before an ordering fault earlier in the tensor
+    bad = good.copy()
+    bad[0, 0, 1] = 0
+    bad[4, 1, 0] = -2
+    assert _validate(qo, kv, 5, 5, 1, table, bad)[0] == -106
+    # the Python wrapper raises AssertionError with the rule's text
+    plan = {"qo_lens_host": qo, "kv_lens_host": kv, "num_qo_heads": 4, "num_kv_heads": 2}
+    from msa_b200.api import _validate_fmha_inputs
+    q = torch.zeros(5, 4, 128)
+    k = torch.zeros(5, 2, 128, 128)
+    _validate_fmha_inputs(q, k, k, plan, torch.from_numpy(table.copy()), torch.from_numpy(good), True)
+    bad = good.copy()
+    bad[2, 1, 2] = 3
+    with pytest.raises(AssertionError, match="out of range"):
+        _validate_fmha_inputs(q, k, k, plan, torch.from_numpy(table.copy()), torch.from_numpy(bad), True)
+    with pytest.raises(AssertionError, match="page pool"):
+        _validate_fmha_inputs(q, k[:4], k[:4], plan, torch.from_numpy(table.copy()), torch.from_numpy(good), True)
+
+
+def test_planner_through_the_c_abi():
+    """msa_plan: tile list, page-table offsets, decode metadata and split choice."""
+    from msa_b200.api import _host_plan
+    work, indptr, tr, tp, splits = _host_plan([2, 1], [300, 1000], None, True, True, 16, 2, kv_block_num=8,
+                                              num_kv_splits=-1, num_sms=148, decode=True)
+    assert indptr.tolist() == [0, 3, 11] and tr.tolist() == [0, 0, 1] and tp.tolist() == [298, 299, 999]
+    assert work.shape == (2, 8) and work[0].tolist() == [1, 2, 1, 0, 1000, 999, 3, 0]
+    assert 1 <= splits <= 8
+    # forced split counts are clamped to the list length; non-causal sees every key
+    assert _host_plan([1], [500], None, True, True, 8, 8, kv_block_num=4, num_kv_splits=9, decode=True)[4] == 4
+    assert _host_plan([3], [500], None, False, True, 8, 8, kv_block_num=4, decode=True)[3].tolist() == [499] * 3
+    # 157 pages in one list: a split count is still found (entries per split may exceed 64)
+    s = _host_plan([1] * 2, [20000] * 2, None, True, True, 16, 2, kv_block_num=157, num_sms=148, decode=True)[4]
+    assert 2 <= s <= 64
+    with pytest.raises(msa_b200.MsaError):
+        _host_plan([1], [-5], None, True, True)
+
+
+def test_c_program_plans_and_validates_through_the_header(tmp_path):
+    """A plain C caller: include/msa_b200.h + libmsa_b200.so, no Python, no GPU."""
+    import shutil
+    import subprocess
+    if shutil.which("gcc") is None:
+        pytest.skip("no gcc")
+    msa_b200.get_lib()
+    src = tmp_path / "plan.c"
+    src.write_text(r'''
+#include <stdio.h>
+#include <stdlib.h>
+#include "msa_b200.h"
+int main(void) {
+  const int32_t qo[2] = {200, 1}, kv[2] = {1000, 4000};
+  msa_plan_desc d = {0};
+  d.batch = 2; d.qo_lens = qo; d.kv_lens = kv; d.qo_offset = NULL; d.causal = 1; d.paged = 1;
+  d.num_qo_heads = 8; d.num_kv_heads = 2; d.kv_block_num = 16; d.num_kv_splits = -1; d.num_sms = 148;
+  int32_t n_work = 0; int64_t total_q = 0, total_pages = 0;
+  if (msa_plan_sizes(&d, &n_work, &total_q, &total_pages) != MSA_OK) return 1;
+  int32_t* work = malloc((size_t)n_work * 8 * sizeof(int32_t));
+  int32_t indptr[3], splits = 0;
+  int32_t* treq = malloc((size_t)total_q * sizeof(int32_t));
+  int32_t* tpos = malloc((size_t)total_q * sizeof(int32_t));
+  if (msa_plan(&d, work, indptr, treq, tpos, &splits) != MSA_OK) return 2;
+  int32_t* table = malloc((size_t)total_pages * sizeof(int32_t));
+  for (int64_t i = 0; i < total_pages; ++i) table[i] = (int32_t)(total_pages - 1 - i);
+  msa_validate_args v = {0};
+  v.batch = 2; v.qo_lens = qo; v.kv_lens = kv; v.total_q = total_q; v.kv_rows = total_pages; v.paged = 1;
+  v.kv_indices = table; v.n_kv_indices = total_pages; v.num_qo_heads = 8; v.num_kv_heads = 2;
+  int64_t where = 0;
+  int ok = msa_validate_inputs(&v, &where);
+  table[5] = (int32_t)total_pages;
+  int bad = msa_validate_inputs(&v, &where);
+  printf("%d %lld %lld %d %d %d %d %d %d %lld %s\n", n_work, (long long)total_q, (long long)total_pages, indptr[2],
+         work[0], tpos[200], splits, ok, bad, (long long)where, msa_error_string(bad));
+  return 0;
+}
+''')
+    exe = tmp_path / "plan"
+    libdir = os.path.join(ROOT, "msa_b200")
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe),
+                    "-L", libdir, "-l:libmsa_b200.so", f"-Wl,-rpath,{libdir}"], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split(maxsplit=10)
+    assert out[:4] == ["3", "201", "40", "40"]
+    assert out[4] == "1" and out[5] == "3999"       # heaviest tile first: the decode token over 4000 keys
+    assert 1 <= int(out[6]) <= 16 and out[7] == "0" and out[8] == "-104" and out[9] == "5"
+    assert "page pool" in out[10]
