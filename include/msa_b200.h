@@ -165,6 +165,9 @@ typedef struct msa_fmha_args {
   int32_t max_ctas;       /* > 0 caps the persistent grid (the reference's usable_SM_count); 0 = one CTA per SM */
   int32_t qk_dim;         /* 0 or 128: all of the head dimension; 64: the score-only pass (out = NULL) uses only the
                              first 64 elements of q and k (a 64-wide proxy zero-padded to 128 costs half) */
+  const uint8_t* tile_uniform;   /* optional, uint8 [n_work, list_heads] from msa_list_uniformity: non-zero where all
+                                    rows of a query tile carry the same page list (the tile's page set is then taken
+                                    from one row instead of 128); NULL = no tile is assumed uniform */
   int64_t max_score_tile_stride; /* elements between consecutive tiles of max_score; 0 = total_q (contiguous) */
   int64_t max_score_head_stride; /* elements between consecutive heads; 0 = max_k_tiles * tile stride.  The two
                                     strides let a call write its tokens into a slice [.., .., t0:t1] of a larger
@@ -172,6 +175,14 @@ typedef struct msa_fmha_args {
 } msa_fmha_args;
 
 int msa_fmha_fwd(const msa_fmha_args* args, void* stream);
+
+/* Optional pre-pass for page-list calls: flags[w * list_heads + h] = 1 iff every row of query tile `w` (an entry of
+ * `work`) has the same list for list head `h`.  MSA selects pages per query block, so the per-token lists of the
+ * reference API (python/fmha_sm100/api.py:207-238) are usually 128 copies of one row; pass the flags as
+ * msa_fmha_args.tile_uniform.  Reads the list tensor once; the reference has no counterpart (its KV-outer kernel
+ * consumes the reverse index instead). */
+int msa_list_uniformity(const int32_t* work, int32_t n_work, const int32_t* kv_block_indexes, int32_t list_heads,
+                        int32_t topk, uint8_t* flags, void* stream);
 
 /* k2q CSR -> per-query page lists, on the device.  The reference's sparse prefill is KV-outer and consumes the
  * reverse index built by `build_k2q_csr` (python/fmha_sm100/cute/sparse_index_utils.py:331-420,

@@ -41,7 +41,7 @@ class FmhaArgs(Structure):
         ("kv_dtype", c_int32), ("paged", c_int32), ("causal", c_int32),
         ("sm_scale", c_float), ("qk_scale", c_float), ("v_scale", c_float),
         ("status", c_void_p), ("max_ctas", c_int32), ("qk_dim", c_int32),
-        ("max_score_tile_stride", c_int64), ("max_score_head_stride", c_int64),
+        ("tile_uniform", c_void_p), ("max_score_tile_stride", c_int64), ("max_score_head_stride", c_int64),
     ]
 
 
@@ -149,6 +149,8 @@ def _bind(lib):
     lib.msa_topk_select.argtypes = [vp, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, vp, vp]
     lib.msa_block_max.restype = c_int32
     lib.msa_block_max.argtypes = [vp, c_int32, c_int32, c_int32, vp, c_int32, vp, vp]
+    lib.msa_list_uniformity.restype = c_int32
+    lib.msa_list_uniformity.argtypes = [vp, c_int32, vp, c_int32, c_int32, vp, vp]
     lib.msa_fmha_fwd.restype = c_int32
     lib.msa_fmha_fwd.argtypes = [POINTER(FmhaArgs), vp]
     lib.msa_decode_workspace_bytes.restype = c_size_t

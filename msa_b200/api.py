@@ -306,6 +306,14 @@ def _run_prefill(q, k, v, plan, kv_indices, kv_block_indexes, qo_offset_t, out, 
     a.num_qo_heads, a.num_kv_heads = plan["num_qo_heads"], plan["num_kv_heads"]
     a.topk = kv_block_indexes.shape[2] if kv_block_indexes is not None else 0
     a.list_heads = kv_block_indexes.shape[1] if kv_block_indexes is not None else 0
+    flags = None
+    if kv_block_indexes is not None and plan["n_work"] > 0:
+        # which query tiles carry one list for all their rows (pages selected per query block): a short device
+        # pass over the lists, then the attention kernel takes such a tile's page set from a single row
+        flags = torch.empty(plan["n_work"] * a.list_heads, dtype=torch.uint8, device=q.device)
+        check(lib.msa_list_uniformity(_ptr(work), plan["n_work"], _ptr(kv_block_indexes), a.list_heads, a.topk,
+                                      _ptr(flags), _stream()), "msa_list_uniformity")
+    a.tile_uniform = _ptr(flags)
     a.max_k_tiles = max_score.shape[1] if max_score is not None else 0
     if max_score is not None:
         # a slice [.., .., t0:t1] of a larger score tensor is written in place through its strides

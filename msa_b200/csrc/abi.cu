@@ -58,6 +58,12 @@ int msa_block_max(const float* max_score, int32_t num_heads, int32_t max_k_tiles
                         static_cast<cudaStream_t>(stream));
 }
 
+int msa_list_uniformity(const int32_t* work, int32_t n_work, const int32_t* kv_block_indexes, int32_t list_heads,
+                        int32_t topk, uint8_t* flags, void* stream) {
+  return msa::list_uniformity(work, n_work, kv_block_indexes, list_heads, topk, flags,
+                              static_cast<cudaStream_t>(stream));
+}
+
 int msa_fmha_fwd(const msa_fmha_args* args, void* stream) {
   return msa::fmha_fwd(args, static_cast<cudaStream_t>(stream));
 }

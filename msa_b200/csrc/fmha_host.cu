@@ -43,6 +43,15 @@ static int make_map(CUtensorMap* m, CUtensorMapDataType dt, int rank, const void
   return r == CUDA_SUCCESS ? MSA_OK : MSA_ERR_DRIVER;
 }
 
+// Output [total_q, Hq, 128] bf16 as 32-row x 32-column boxes (64-byte rows, 64-byte swizzle): one per softmax warp
+// and column quarter
+static int make_o_map(CUtensorMap* m, const void* o, int64_t total_q, int hq) {
+  const uint64_t dims[3] = {128, static_cast<uint64_t>(hq), static_cast<uint64_t>(total_q)};
+  const uint64_t strides[2] = {256, static_cast<uint64_t>(hq) * 256};
+  const uint32_t box[3] = {32, 1, 32};
+  return make_map(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, o, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
+}
+
 static int make_q_map(CUtensorMap* m, const void* q, int64_t total_q, int hq) {
   const uint64_t dims[3] = {128, static_cast<uint64_t>(hq), static_cast<uint64_t>(total_q)};
   const uint64_t strides[2] = {256, static_cast<uint64_t>(hq) * 256};
@@ -77,8 +86,8 @@ static long long* g_timing_buffer = nullptr;
 void set_timing_buffer(void* ptr) { g_timing_buffer = static_cast<long long*>(ptr); }
 
 template <int NT, int KVMODE>
-static int launch_fmha(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FmhaParams& p,
-                       int max_ctas, cudaStream_t st) {
+static int launch_fmha(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
+                       const FmhaParams& p, int max_ctas, cudaStream_t st) {
   using Cfg = FmhaCfg<NT, KVMODE>;
   static DeviceSetup setup;
   int num_sms = 0;
@@ -99,7 +108,7 @@ static int launch_fmha(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
   // persistent: one CTA per SM walks the item list with stride gridDim.x; max_ctas > 0 caps the grid
   int ctas = p.n_items < num_sms ? p.n_items : num_sms;
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
-  fmha_fwd_kernel<NT, KVMODE><<<static_cast<unsigned>(ctas), Cfg::kThreads, smem, st>>>(mq, mk, mv, p);
+  fmha_fwd_kernel<NT, KVMODE><<<static_cast<unsigned>(ctas), Cfg::kThreads, smem, st>>>(mq, mk, mv, mo, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -134,6 +143,7 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
   p.work = reinterpret_cast<const int4*>(a->work);
   p.kv_indices = a->kv_indices;
   p.kv_block_indexes = a->kv_block_indexes;
+  p.tile_uniform = sparse ? a->tile_uniform : nullptr;
   p.k_scale_bytes = a->k_scale_128x4;
   p.v_scale_bytes = a->v_scale_128x4;
   p.k_raw = static_cast<const uint8_t*>(a->k);
@@ -164,8 +174,11 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
   if (n_items > 0x7fffffffLL) return MSA_ERR_TOO_LARGE;
   p.n_items = static_cast<int>(n_items);
 
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk, mv, mo;
   int rc = make_q_map(&mq, a->q, a->total_q, p.Hq);
+  if (rc != MSA_OK) return rc;
+  // score-only calls have no output: the map is never used then, but must be a valid one
+  rc = make_o_map(&mo, a->out != nullptr ? a->out : a->q, a->total_q, p.Hq);
   if (rc != MSA_OK) return rc;
   if (a->kv_dtype == MSA_KV_NVFP4) {
     mk = mq;  // pages are fetched with untiled bulk copies
@@ -178,14 +191,51 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
     if (rc != MSA_OK) return rc;
   }
   switch (a->kv_dtype * 2 + (nt - 1)) {
-    case 0: return launch_fmha<1, KV_BF16>(mq, mk, mv, p, a->max_ctas, st);
-    case 1: return launch_fmha<2, KV_BF16>(mq, mk, mv, p, a->max_ctas, st);
-    case 2: return launch_fmha<1, KV_FP8>(mq, mk, mv, p, a->max_ctas, st);
-    case 3: return launch_fmha<2, KV_FP8>(mq, mk, mv, p, a->max_ctas, st);
-    case 4: return launch_fmha<1, KV_NVFP4>(mq, mk, mv, p, a->max_ctas, st);
-    case 5: return launch_fmha<2, KV_NVFP4>(mq, mk, mv, p, a->max_ctas, st);
+    case 0: return launch_fmha<1, KV_BF16>(mq, mk, mv, mo, p, a->max_ctas, st);
+    case 1: return launch_fmha<2, KV_BF16>(mq, mk, mv, mo, p, a->max_ctas, st);
+    case 2: return launch_fmha<1, KV_FP8>(mq, mk, mv, mo, p, a->max_ctas, st);
+    case 3: return launch_fmha<2, KV_FP8>(mq, mk, mv, mo, p, a->max_ctas, st);
+    case 4: return launch_fmha<1, KV_NVFP4>(mq, mk, mv, mo, p, a->max_ctas, st);
+    case 5: return launch_fmha<2, KV_NVFP4>(mq, mk, mv, mo, p, a->max_ctas, st);
   }
   return MSA_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------------------
+// Which query tiles have one page list for all their rows?  MSA selects pages per query block, so the per-token
+// lists the API takes are usually 128 copies of one row; the attention kernel then builds a tile's page bitmap
+// from a single row instead of 128.  One CTA per (tile, list head): row r is compared with row 0.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) list_uniform_kernel(const int4* __restrict__ work,
+                                                          const int* __restrict__ lists, int list_heads, int topk,
+                                                          uint8_t* __restrict__ flags) {
+  const int wi = blockIdx.x, lh = blockIdx.y, r = threadIdx.x;
+  const int4 w = __ldg(work + 2 * wi);   // {request, first token, rows, first local token}
+  const int* row0 = lists + (static_cast<size_t>(w.y) * list_heads + lh) * topk;
+  const int* mine = lists + (static_cast<size_t>(w.y + r) * list_heads + lh) * topk;
+  int same = 1;
+  if (r > 0 && r < w.z) {
+    if ((topk & 3) == 0) {
+      for (int e = 0; e < topk; e += 4) {
+        const int4 a = __ldg(reinterpret_cast<const int4*>(row0 + e)), b = __ldg(reinterpret_cast<const int4*>(mine + e));
+        same &= (a.x == b.x) & (a.y == b.y) & (a.z == b.z) & (a.w == b.w);
+      }
+    } else {
+      for (int e = 0; e < topk; ++e) same &= __ldg(row0 + e) == __ldg(mine + e);
+    }
+  }
+  same = __syncthreads_and(same);
+  if (r == 0) flags[static_cast<size_t>(wi) * list_heads + lh] = static_cast<uint8_t>(same);
+}
+
+int list_uniformity(const int32_t* work, int n_work, const int32_t* lists, int list_heads, int topk, uint8_t* flags,
+                    cudaStream_t st) {
+  if (work == nullptr || lists == nullptr || flags == nullptr || list_heads <= 0 || list_heads > 65535 || topk <= 0)
+    return MSA_ERR_INVALID;
+  if (n_work <= 0) return MSA_OK;
+  list_uniform_kernel<<<dim3(n_work, list_heads), 128, 0, st>>>(reinterpret_cast<const int4*>(work), lists, list_heads,
+                                                                topk, flags);
+  return static_cast<int>(cudaGetLastError());
 }
 
 // ---------------------------------------------------------------------------

@@ -53,7 +53,7 @@ enum KvMode : int { KV_BF16 = 0, KV_FP8 = 1, KV_NVFP4 = 2 };
   if ((cond) && p.timing != nullptr) {                                                        \
     for (int ti = lo; ti < hi; ++ti) p.timing[static_cast<size_t>(blockIdx.x) * 16 + ti] = tacc[ti]; \
   }
-#define MSA_TRACE(slot, iter, val) if (blockIdx.x == 0 && p.timing != nullptr && (iter) >= 64 && (iter) < 80) p.timing[4096 + ((iter) - 64) * 16 + (slot)] = (val);
+#define MSA_TRACE(slot, iter, val) if (blockIdx.x == 0 && p.timing != nullptr && (iter) >= 56 && (iter) < 88) p.timing[4096 + ((iter) - 56) * 16 + (slot)] = (val);
 #else
 #define MSA_TRACE(slot, iter, val)
 #define MSA_TDECL
@@ -71,6 +71,7 @@ struct FmhaParams {
                                  // (request-local)}, {kv_len, causal offset, first page-table slot | first K/V token, 0}
   const int* kv_indices;         // flat page table (paged)
   const int* kv_block_indexes;   // [total_q, list_heads, topk] request-local page ids, ascending, -1 tail; or null
+  const uint8_t* tile_uniform;   // [n_work, list_heads]: 1 = every row of the query tile has the same list; or null
   const uint8_t* k_scale_bytes;  // NVFP4: e4m3 block scales in 128x4 tiles, one 1 KiB block per (page, head)
   const uint8_t* v_scale_bytes;
   const uint8_t* k_raw;          // NVFP4 raw page storage
@@ -92,11 +93,14 @@ struct FmhaCfg {
   static constexpr bool kVConvert = kQuant;                 // V is dequantised by the convert warps
   static constexpr bool kQConvert = kQuant;                 // softmax threads rewrite Q (f16, or e4m3 hi/lo)
   static constexpr int kKBytes = kKDirectFp8 ? kHalfBytes : kTileBytes;
-  static constexpr int kKStages = kKDirectFp8 ? 3 : 2;
+  static constexpr int kKStages = 2;
   static constexpr int kVStages = 2;
   static constexpr int kRawStages = kQuant ? 2 : 0;
   static constexpr int kRawBytes = KVMODE == KV_NVFP4 ? 10240 : 16384;
   static constexpr int kSoftmaxWarps = 4 * NT;
+  // output through shared-memory staging + TMA stores; the two-head NVFP4 variant has no shared memory left
+  // for the staging buffers and keeps per-row stores
+  static constexpr bool kStageOut = !(KVMODE == KV_NVFP4 && NT == 2);
   static constexpr int kProducerWarp = kSoftmaxWarps;
   static constexpr int kMmaWarp = kSoftmaxWarps + 1;
   static constexpr int kCvtWarp0 = kSoftmaxWarps + 2;
@@ -126,6 +130,10 @@ struct __align__(1024) FmhaSmem {
   uint8_t k[Cfg::kKStages][Cfg::kKBytes];
   uint8_t v[Cfg::kVStages][kTileBytes];
   uint8_t raw[Cfg::kRawStages > 0 ? Cfg::kRawStages : 1][Cfg::kRawStages > 0 ? Cfg::kRawBytes : 16];
+  // output staging, one 32-row x 32-column bf16 piece (64-byte rows, 64-byte swizzle) per softmax warp: the
+  // epilogue writes its rows here and a TMA store moves them out, instead of 16-byte stores scattered over
+  // rows that lie num_qo_heads * 256 bytes apart
+  alignas(1024) uint8_t o_stage[Cfg::kStageOut ? Cfg::kSoftmaxWarps : 1][Cfg::kStageOut ? 2048 : 16];
   uint64_t q_full, q_ready, q_empty;
   uint64_t k_full[Cfg::kKStages], k_empty[Cfg::kKStages];
   uint64_t v_full[Cfg::kVStages], v_empty[Cfg::kVStages];
@@ -349,7 +357,8 @@ __device__ __forceinline__ void issue_pv_stage(Smem& sm, int stage, uint32_t acc
 template <int NT, int KVMODE>
 __global__ void __launch_bounds__(FmhaCfg<NT, KVMODE>::kThreads, 1)
 fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                const __grid_constant__ CUtensorMap tmap_v, const FmhaParams p) {
+                const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
+                const FmhaParams p) {
   using Cfg = FmhaCfg<NT, KVMODE>;
   using Smem = FmhaSmem<NT, KVMODE>;
   constexpr int NK = Cfg::kKStages, NV = Cfg::kVStages;
@@ -404,6 +413,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     tma_prefetch_desc(&tmap_q);
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
+    tma_prefetch_desc(&tmap_o);
   }
   tc_fence_before();
   __syncthreads();
@@ -587,6 +597,11 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       if (!ok) return;
       const float inv = (pend.l_sum > 0.f) ? p.out_scale * kGain / pend.l_sum : 0.f;
       __nv_bfloat16* orow = p.out + (static_cast<size_t>(pend.tok) * p.Hq + pend.h) * 128;
+      // a warp whose 32 rows all exist stages its piece in shared memory and lets TMA write it (rows of other
+      // requests follow a partial tile in the output, so such a tile keeps the per-row stores)
+      const bool via_tma = Cfg::kStageOut && __all_sync(0xffffffffu, pend.row_valid);
+      uint8_t* stage = sm.o_stage[Cfg::kStageOut ? warp : 0];
+      const int row32 = r & 31;
       uint32_t rg[32];
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {   // not unrolled: once per item, and the kernel's code should stay cache-sized
@@ -597,17 +612,31 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
           for (int e = 0; e < 32; ++e) rg[e] = 0u;
         }
-        if (pend.row_valid) {
+        uint4 o[4];
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          o[v].x = pack_bf16x2(__uint_as_float(rg[v * 8 + 0]) * inv, __uint_as_float(rg[v * 8 + 1]) * inv);
+          o[v].y = pack_bf16x2(__uint_as_float(rg[v * 8 + 2]) * inv, __uint_as_float(rg[v * 8 + 3]) * inv);
+          o[v].z = pack_bf16x2(__uint_as_float(rg[v * 8 + 4]) * inv, __uint_as_float(rg[v * 8 + 5]) * inv);
+          o[v].w = pack_bf16x2(__uint_as_float(rg[v * 8 + 6]) * inv, __uint_as_float(rg[v * 8 + 7]) * inv);
+        }
+        if (via_tma) {
+          if (lane == 0) tma_store_wait_read();   // the previous piece has left the staging buffer
+          __syncwarp();
+          // 64-byte swizzle: 16-byte chunk v of row i sits at chunk v ^ ((i >> 1) & 3)
+#pragma unroll
+          for (int v = 0; v < 4; ++v)
+            *reinterpret_cast<uint4*>(stage + row32 * 64 + ((v ^ ((row32 >> 1) & 3)) << 4)) = o[v];
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_3d(&tmap_o, stage, c * 32, pend.h, pend.tok - row32);
+            tma_store_commit();
+          }
+        } else if (pend.row_valid) {
           uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint4 o;
-            o.x = pack_bf16x2(__uint_as_float(rg[v * 8 + 0]) * inv, __uint_as_float(rg[v * 8 + 1]) * inv);
-            o.y = pack_bf16x2(__uint_as_float(rg[v * 8 + 2]) * inv, __uint_as_float(rg[v * 8 + 3]) * inv);
-            o.z = pack_bf16x2(__uint_as_float(rg[v * 8 + 4]) * inv, __uint_as_float(rg[v * 8 + 5]) * inv);
-            o.w = pack_bf16x2(__uint_as_float(rg[v * 8 + 6]) * inv, __uint_as_float(rg[v * 8 + 7]) * inv);
-            dst[v] = o;
-          }
+          for (int v = 0; v < 4; ++v) dst[v] = o[v];
         }
       }
       if (p.lse != nullptr && pend.row_valid) {
@@ -773,12 +802,16 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // ---- hand the tensor core the next item's Q before draining this item's O -------
       const int next_item = item + item_step;
       MSA_TBEGIN
+      if (r == 0 && t == 0) { MSA_TRACE(8, it_total, clock64()) }
       if (next_item < p.n_items && ok) setup(next_item, j + 1);
+      if (r == 0 && t == 0) { MSA_TRACE(9, it_total, clock64()) }
       MSA_TEND(2)
       MSA_TBEGIN
       epilogue();
+      if (r == 0 && t == 0) { MSA_TRACE(10, it_total, clock64()) }
       MSA_TEND(10)
     }
+    if (lane == 0) tma_store_wait_all();   // this warp's output pieces have left shared memory and are written
     MSA_TFLUSH(tid == 0, 0, 3)
     MSA_TFLUSH(tid == 0, 10, 11)
   } else {
@@ -789,8 +822,11 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // =======================================================================
       bool ok = true;
       uint32_t n_q = 0, k_seq = 0, v_seq = 0, raw_seq = 0;
+      uint32_t pg_total = 0;   // pages issued so far (trace index of an item's first iteration)
+      (void)pg_total;
       int j = 0;
       for (int item = item0; item < p.n_items && ok; item += item_step, ++j) {
+        if (lane == 0) { MSA_TRACE(11, pg_total, clock64()) }
         const ItemInfo info = load_item(p, item, NT);
         const int b = j & 1;
         if (info.oversize && lane == 0) atomicExch(p.status, MSA_ERR_UNSUPPORTED);
@@ -804,15 +840,29 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           __syncwarp();
           // the union of the pages any row of the tile selected and can see
           const int lh = (p.list_heads == p.Hkv) ? info.g : info.h0;
-          for (int rr = lane; rr < info.rows; rr += 32) {
+          const int npr = info.n_pages_req;
+          uint32_t* bmw = sm.bitmap[b];
+          const bool uniform = p.tile_uniform != nullptr &&
+                               __ldg(p.tile_uniform + static_cast<size_t>(item / p.n_head_groups) * p.list_heads + lh) != 0;
+          if (uniform) {
+            // one list for the whole tile (the usual case: pages are selected per query block): its entries,
+            // one per lane, cut at what the tile's last row can see
             int lim = info.kv_len - 1;
-            if (p.causal) lim = min(lim, info.qloc0 + rr + info.qo_off);
-            const int* list = p.kv_block_indexes + (static_cast<size_t>(info.tok0 + rr) * p.list_heads + lh) * p.topk;
-            const int npr = info.n_pages_req;
-            uint32_t* bmw = sm.bitmap[b];
-            for_each_list_entry(list, p.topk, [&](int, int pg) {
-              if (pg < npr && (pg << 7) <= lim) atomicOr(&bmw[pg >> 5], 1u << (pg & 31));
-            });
+            if (p.causal) lim = min(lim, info.qloc0 + info.rows - 1 + info.qo_off);
+            const int* list = p.kv_block_indexes + (static_cast<size_t>(info.tok0) * p.list_heads + lh) * p.topk;
+            for (int e = lane; e < p.topk; e += 32) {
+              const int pg = __ldg(list + e);
+              if (pg >= 0 && pg < npr && (pg << 7) <= lim) atomicOr(&bmw[pg >> 5], 1u << (pg & 31));
+            }
+          } else {
+            for (int rr = lane; rr < info.rows; rr += 32) {
+              int lim = info.kv_len - 1;
+              if (p.causal) lim = min(lim, info.qloc0 + rr + info.qo_off);
+              const int* list = p.kv_block_indexes + (static_cast<size_t>(info.tok0 + rr) * p.list_heads + lh) * p.topk;
+              for_each_list_entry(list, p.topk, [&](int, int pg) {
+                if (pg < npr && (pg << 7) <= lim) atomicOr(&bmw[pg >> 5], 1u << (pg & 31));
+              });
+            }
           }
           __syncwarp();
           int cnt = 0;
@@ -826,6 +876,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
         MSA_TEND(11)
         if (lane != 0) continue;
+        MSA_TRACE(12, pg_total, clock64())
         PageWalk walk;
         walk.init(p.sparse, sm.bitmap[b], info.walk_n);
         int page = walk.next();
@@ -836,6 +887,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         MSA_TEND(12)
         if (!ok) break;
         ++n_q;
+        MSA_TRACE(13, pg_total, clock64())
         mbar_expect_tx(&sm.q_full, NT * kTileBytes);
         for (int t = 0; t < NT; ++t) {
           tma_load_3d(sm.q[t], &tmap_q, &sm.q_full, 0, info.h0 + t, info.tok0);
@@ -844,6 +896,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const int page_base = p.paged ? info.kv_base : 0;
         const int tok_base = p.paged ? 0 : info.kv_base;
         for (; page >= 0 && ok; page = walk.next()) {
+          ++pg_total;
           const int phys = p.paged ? __ldg(p.kv_indices + page_base + page) : 0;
           const int tok_k = tok_base + (page << 7);
           const size_t tile = static_cast<size_t>(phys) * p.Hkv + info.g;
@@ -941,6 +994,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           MSA_TBEGIN
           ok = mbar_wait(Cfg::kQConvert ? &sm.q_ready : &sm.q_full, n_q & 1, abort_flag);
           MSA_TEND(14)
+          if (lane == 0) { MSA_TRACE(14, it_total, clock64()) }
           ++n_q;
           if (!p.do_pv) {
             // Score-only pass: nothing but Q K^T, one page after the other into alternating S buffers; the

@@ -57,12 +57,13 @@ def alloc_fp8_cache(num_pages: int, num_kv_heads: int, device) -> Tuple[torch.Te
 
 
 def alloc_nvfp4_cache(num_pages: int, num_kv_heads: int, device):
-    """``(k_data, v_data, k_block_scales, v_block_scales)``: uint8 [pages, Hkv, 128, 64] and the flat 128x4-tiled
-    e4m3 scale storage over [pages * Hkv * 128, 8]."""
+    """``(k_data, v_data, k_block_scales, v_block_scales)``: uint8 [pages, Hkv, 128, 64] and the 128x4-tiled
+    e4m3 scale storage, uint8 [pages * Hkv * 128, 8] (the rank-2 shape the reference's NVFP4 entry points take,
+    python/fmha_sm100/cute/interface.py:355-416)."""
     shape = (num_pages, num_kv_heads, PAGE, HEAD_DIM // 2)
-    nscale = num_pages * num_kv_heads * PAGE * (HEAD_DIM // 16)
+    sshape = (num_pages * num_kv_heads * PAGE, HEAD_DIM // 16)
     mk = lambda *s: torch.zeros(*s, dtype=torch.uint8, device=device)  # noqa: E731
-    return mk(shape), mk(shape), mk(nscale), mk(nscale)
+    return mk(shape), mk(shape), mk(sshape), mk(sshape)
 
 
 def _append(fmt, k_new, v_new, k_cache, v_cache, k_bs, v_bs, slots, k_scale, v_scale):

@@ -39,7 +39,7 @@ def nvfp4_scale_128x4_offset(row: torch.Tensor, col: torch.Tensor, scale_cols: i
 @dataclass
 class Nvfp4QuantizedTensor:
     data: torch.Tensor          # uint8 [..., D/2]
-    scale_128x4: torch.Tensor   # uint8 flat, e4m3 bits
+    scale_128x4: torch.Tensor   # uint8 [round_up(rows, 128), round_up(D/16, 4)], e4m3 bits in 128x4-tiled storage
     global_scale: torch.Tensor  # float32 [1]
     logical_scale_shape: Tuple[int, int]
     original_shape: Tuple[int, ...]
@@ -78,7 +78,7 @@ def quantize_bf16_to_nvfp4_128x4(x: torch.Tensor) -> Nvfp4QuantizedTensor:
     r = torch.arange(rows, device=x.device).view(-1, 1).expand(rows, scols)
     c = torch.arange(scols, device=x.device).view(1, -1).expand(rows, scols)
     sflat[nvfp4_scale_128x4_offset(r, c, scols).reshape(-1)] = bscale.view(torch.uint8).reshape(-1)
-    return Nvfp4QuantizedTensor(data=data.view(*x.shape[:-1], D // 2), scale_128x4=sflat,
+    return Nvfp4QuantizedTensor(data=data.view(*x.shape[:-1], D // 2), scale_128x4=sflat.view(rows_pad, cols_pad),
                                 global_scale=torch.tensor([gscale], dtype=torch.float32, device=x.device),
                                 logical_scale_shape=(rows, scols), original_shape=tuple(x.shape))
 

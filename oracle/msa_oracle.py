@@ -467,7 +467,7 @@ def kv_append_nvfp4(k_new, v_new, k_cache, v_cache, k_block_scales, v_block_scal
         col = torch.arange(D // NVFP4_BLOCK).view(1, 1, -1)
         off = nvfp4_scale_offset(row.expand(-1, hkv, D // NVFP4_BLOCK), col.expand(sl.numel(), hkv, -1),
                                  D // NVFP4_BLOCK)
-        bsc[off.reshape(-1)] = bscale.view(torch.uint8)[ok].reshape(-1)
+        bsc.view(-1)[off.reshape(-1)] = bscale.view(torch.uint8)[ok].reshape(-1)   # flat or [rows, 8] storage
 
 
 # ---------------------------------------------------------------------------
