@@ -146,6 +146,12 @@ struct __align__(1024) FmhaSmem {
   int abort;
   int item_pages[2];   // pages in the walk of the item that owns bitmap buffer b (sparse)
   uint32_t bitmap[2][kBitmapWords];
+  // Sparse pass, published by the producer together with the bitmap of buffer b so that no role waits on global
+  // memory at an item boundary: the item's work record and, for a tile whose rows all carry one list, that
+  // list's cursor (index and page of its last entry inside the request, page of the entry before it).
+  int4 item_work[2][2];
+  int item_uniform[2];
+  int uni_cur[2][4];
 };
 
 template <int NT, int KVMODE>
@@ -191,12 +197,10 @@ struct ItemInfo {
   bool oversize;
 };
 
-__device__ __forceinline__ ItemInfo load_item(const FmhaParams& p, int item, int nt) {
+// w, w2: the two int4 halves of the item's work record
+__device__ __forceinline__ ItemInfo decode_item(const FmhaParams& p, int item, int nt, const int4 w, const int4 w2) {
   ItemInfo it;
   const int hg = item % p.n_head_groups;  // head group fastest: CTAs running side by side share K/V pages
-  const int wi = item / p.n_head_groups;
-  const int4 w = __ldg(p.work + 2 * wi);
-  const int4 w2 = __ldg(p.work + 2 * wi + 1);
   it.req = w.x;
   it.tok0 = w.y;
   it.rows = w.z;
@@ -216,6 +220,10 @@ __device__ __forceinline__ ItemInfo load_item(const FmhaParams& p, int item, int
   const int n_dense = kv_vis > 0 ? (kv_vis + 127) >> 7 : 0;
   it.walk_n = p.sparse ? it.n_pages_req : n_dense;
   return it;
+}
+__device__ __forceinline__ ItemInfo load_item(const FmhaParams& p, int item, int nt) {
+  const int wi = item / p.n_head_groups;
+  return decode_item(p, item, nt, __ldg(p.work + 2 * wi), __ldg(p.work + 2 * wi + 1));
 }
 
 // Calls f(entry index, page) for the leading valid entries of one page list (ascending ids, -1 tail):
@@ -468,8 +476,14 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 
     // prepares item `item` (index j in this CTA's sequence): row visibility, list cursor, Q rewrite
     auto setup = [&](int item, int j) {
-      nx.info = load_item(p, item, NT);
       nx.bm = j & 1;
+      if (p.sparse) {
+        // the producer published the item's work record (and a uniform tile's list cursor) with the bitmap
+        ok = ok && mbar_wait(&sm.bm_full[nx.bm], (j >> 1) & 1, abort_flag);
+        nx.info = decode_item(p, item, NT, sm.item_work[nx.bm][0], sm.item_work[nx.bm][1]);
+      } else {
+        nx.info = load_item(p, item, NT);
+      }
       nx.row_valid = r < nx.info.rows;
       nx.limit_base = -1;
       nx.list = nullptr;
@@ -481,10 +495,14 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         nx.limit_base = nx.info.kv_len - 1;
         if (p.causal) nx.limit_base = min(nx.limit_base, nx.info.qloc0 + r + nx.info.qo_off);
       }
-      if (p.sparse) {
-        if (nx.row_valid) {
-          const int lh = (p.list_heads == p.Hkv) ? nx.info.g : (nx.info.h0 + t);
-          nx.list = p.kv_block_indexes + (static_cast<size_t>(nx.info.tok0 + r) * p.list_heads + lh) * p.topk;
+      if (p.sparse && nx.row_valid) {
+        const int lh = (p.list_heads == p.Hkv) ? nx.info.g : (nx.info.h0 + t);
+        nx.list = p.kv_block_indexes + (static_cast<size_t>(nx.info.tok0 + r) * p.list_heads + lh) * p.topk;
+        if (sm.item_uniform[nx.bm]) {
+          nx.cur = sm.uni_cur[nx.bm][0];
+          nx.cur_page = sm.uni_cur[nx.bm][1];
+          nx.prev_page = sm.uni_cur[nx.bm][2];
+        } else {
           int cur = -1, cur_page = -1, prev_page = -1;
           const int npr = nx.info.n_pages_req;
           for_each_list_entry(nx.list, p.topk, [&](int e, int pg) {
@@ -498,7 +516,6 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           nx.cur_page = cur_page;
           nx.prev_page = prev_page;
         }
-        ok = ok && mbar_wait(&sm.bm_full[nx.bm], (j >> 1) & 1, abort_flag);
       }
       nx.walk.init(p.sparse, sm.bitmap[nx.bm], nx.info.walk_n);
       nx.first_page = ok ? nx.walk.next() : -1;
@@ -824,79 +841,115 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       uint32_t n_q = 0, k_seq = 0, v_seq = 0, raw_seq = 0;
       uint32_t pg_total = 0;   // pages issued so far (trace index of an item's first iteration)
       (void)pg_total;
+      // Sparse pass: bitmap, page count and metadata of item `item` (the jj-th of this CTA) into buffer jj & 1.
+      // All lanes take part.  It runs one item ahead, in the middle of the previous item's page loads (when the
+      // rings are full and the warp would only wait), so its global-memory latency is off every critical path.
+      auto build_bitmap = [&](int item, int jj) {
+        const int b = jj & 1;
+        const int wi = item / p.n_head_groups;
+        const int4 w = __ldg(p.work + 2 * wi), w2 = __ldg(p.work + 2 * wi + 1);
+        const ItemInfo info = decode_item(p, item, NT, w, w2);
+        const int lh = (p.list_heads == p.Hkv) ? info.g : info.h0;
+        const bool uniform = p.tile_uniform != nullptr &&
+                             __ldg(p.tile_uniform + static_cast<size_t>(wi) * p.list_heads + lh) != 0;
+        if (info.oversize && lane == 0) atomicExch(p.status, MSA_ERR_UNSUPPORTED);
+        // the buffer was used by item jj - 2: wait until every walker released it
+        ok = mbar_wait(&sm.bm_empty[b], ((jj >> 1) & 1) ^ 1, abort_flag);
+        if (!ok) return;
+        const int words = (info.n_pages_req + 31) >> 5;
+        for (int x = lane; x < words; x += 32) sm.bitmap[b][x] = 0;
+        __syncwarp();
+        // the union of the pages any row of the tile selected and can see
+        const int npr = info.n_pages_req;
+        uint32_t* bmw = sm.bitmap[b];
+        int cur = -1, cur_page = -1, prev_page = -1;
+        if (uniform) {
+          // one list for the whole tile (the usual case: pages are selected per query block): its entries,
+          // one per lane, cut at what the tile's last row can see
+          int lim = info.kv_len - 1;
+          if (p.causal) lim = min(lim, info.qloc0 + info.rows - 1 + info.qo_off);
+          const int* list = p.kv_block_indexes + (static_cast<size_t>(info.tok0) * p.list_heads + lh) * p.topk;
+          for (int e0 = 0; e0 < p.topk; e0 += 32) {
+            const int e = e0 + lane;
+            const int pg = e < p.topk ? __ldg(list + e) : -1;
+            const bool inside = pg >= 0 && pg < npr;
+            if (inside && (pg << 7) <= lim) atomicOr(&bmw[pg >> 5], 1u << (pg & 31));
+            // cursor: the last entry inside the request and the page before it (entries ascend, -1 only at the tail)
+            const uint32_t m = __ballot_sync(0xffffffffu, inside);
+            if (m != 0u) {
+              const int last = 31 - __clz(m);
+              const int pg_last = __shfl_sync(0xffffffffu, pg, last);
+              const int pg_before = __shfl_sync(0xffffffffu, pg, last > 0 ? last - 1 : 0);
+              prev_page = last > 0 ? pg_before : cur_page;
+              cur = e0 + last;
+              cur_page = pg_last;
+            }
+          }
+        } else {
+          for (int rr = lane; rr < info.rows; rr += 32) {
+            int lim = info.kv_len - 1;
+            if (p.causal) lim = min(lim, info.qloc0 + rr + info.qo_off);
+            const int* list = p.kv_block_indexes + (static_cast<size_t>(info.tok0 + rr) * p.list_heads + lh) * p.topk;
+            for_each_list_entry(list, p.topk, [&](int, int pg) {
+              if (pg < npr && (pg << 7) <= lim) atomicOr(&bmw[pg >> 5], 1u << (pg & 31));
+            });
+          }
+        }
+        __syncwarp();
+        int cnt = 0;
+        for (int x = lane; x < words; x += 32) cnt += __popc(sm.bitmap[b][x]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+        if (lane == 0) {
+          sm.item_pages[b] = cnt;
+          sm.item_work[b][0] = w;
+          sm.item_work[b][1] = w2;
+          sm.item_uniform[b] = uniform ? 1 : 0;
+          sm.uni_cur[b][0] = cur;
+          sm.uni_cur[b][1] = cur_page;
+          sm.uni_cur[b][2] = prev_page;
+        }
+        __threadfence_block();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.bm_full[b]);
+      };
+      MSA_TBEGIN
+      if (p.sparse && item0 < p.n_items) build_bitmap(item0, 0);
+      MSA_TEND(11)
       int j = 0;
       for (int item = item0; item < p.n_items && ok; item += item_step, ++j) {
         if (lane == 0) { MSA_TRACE(11, pg_total, clock64()) }
-        const ItemInfo info = load_item(p, item, NT);
         const int b = j & 1;
-        if (info.oversize && lane == 0) atomicExch(p.status, MSA_ERR_UNSUPPORTED);
-        MSA_TBEGIN
-        if (p.sparse) {
-          // the buffer was used by item j - 2: wait until every walker released it
-          ok = mbar_wait(&sm.bm_empty[b], ((j >> 1) & 1) ^ 1, abort_flag);
-          if (!ok) break;
-          const int words = (info.n_pages_req + 31) >> 5;
-          for (int w = lane; w < words; w += 32) sm.bitmap[b][w] = 0;
-          __syncwarp();
-          // the union of the pages any row of the tile selected and can see
-          const int lh = (p.list_heads == p.Hkv) ? info.g : info.h0;
-          const int npr = info.n_pages_req;
-          uint32_t* bmw = sm.bitmap[b];
-          const bool uniform = p.tile_uniform != nullptr &&
-                               __ldg(p.tile_uniform + static_cast<size_t>(item / p.n_head_groups) * p.list_heads + lh) != 0;
-          if (uniform) {
-            // one list for the whole tile (the usual case: pages are selected per query block): its entries,
-            // one per lane, cut at what the tile's last row can see
-            int lim = info.kv_len - 1;
-            if (p.causal) lim = min(lim, info.qloc0 + info.rows - 1 + info.qo_off);
-            const int* list = p.kv_block_indexes + (static_cast<size_t>(info.tok0) * p.list_heads + lh) * p.topk;
-            for (int e = lane; e < p.topk; e += 32) {
-              const int pg = __ldg(list + e);
-              if (pg >= 0 && pg < npr && (pg << 7) <= lim) atomicOr(&bmw[pg >> 5], 1u << (pg & 31));
-            }
-          } else {
-            for (int rr = lane; rr < info.rows; rr += 32) {
-              int lim = info.kv_len - 1;
-              if (p.causal) lim = min(lim, info.qloc0 + rr + info.qo_off);
-              const int* list = p.kv_block_indexes + (static_cast<size_t>(info.tok0 + rr) * p.list_heads + lh) * p.topk;
-              for_each_list_entry(list, p.topk, [&](int, int pg) {
-                if (pg < npr && (pg << 7) <= lim) atomicOr(&bmw[pg >> 5], 1u << (pg & 31));
-              });
-            }
-          }
-          __syncwarp();
-          int cnt = 0;
-          for (int w = lane; w < words; w += 32) cnt += __popc(sm.bitmap[b][w]);
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
-          if (lane == 0) sm.item_pages[b] = cnt;
-          __threadfence_block();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&sm.bm_full[b]);
-        }
-        MSA_TEND(11)
-        if (lane != 0) continue;
-        MSA_TRACE(12, pg_total, clock64())
+        const ItemInfo info = p.sparse ? decode_item(p, item, NT, sm.item_work[b][0], sm.item_work[b][1])
+                                       : load_item(p, item, NT);
+        const int next_item = item + item_step;
+        bool next_pending = p.sparse && next_item < p.n_items;
+        if (lane == 0) { MSA_TRACE(12, pg_total, clock64()) }
         PageWalk walk;
         walk.init(p.sparse, sm.bitmap[b], info.walk_n);
         int page = walk.next();
-        if (page < 0) continue;
-        // Q of this item: the tile buffer is free once the previous item's last QK has completed
-        MSA_TBEGIN
-        ok = mbar_wait(&sm.q_empty, (n_q & 1) ^ 1, abort_flag);
-        MSA_TEND(12)
-        if (!ok) break;
-        ++n_q;
-        MSA_TRACE(13, pg_total, clock64())
-        mbar_expect_tx(&sm.q_full, NT * kTileBytes);
-        for (int t = 0; t < NT; ++t) {
-          tma_load_3d(sm.q[t], &tmap_q, &sm.q_full, 0, info.h0 + t, info.tok0);
-          tma_load_3d(sm.q[t] + kHalfBytes, &tmap_q, &sm.q_full, 64, info.h0 + t, info.tok0);
+        if (page >= 0) {
+          // Q of this item: the tile buffer is free once the previous item's last QK has completed
+          if (lane == 0) {
+            MSA_TBEGIN
+            ok = mbar_wait(&sm.q_empty, (n_q & 1) ^ 1, abort_flag);
+            MSA_TEND(12)
+            if (ok) {
+              MSA_TRACE(13, pg_total, clock64())
+              mbar_expect_tx(&sm.q_full, NT * kTileBytes);
+              for (int t = 0; t < NT; ++t) {
+                tma_load_3d(sm.q[t], &tmap_q, &sm.q_full, 0, info.h0 + t, info.tok0);
+                tma_load_3d(sm.q[t] + kHalfBytes, &tmap_q, &sm.q_full, 64, info.h0 + t, info.tok0);
+              }
+            }
+          }
+          ++n_q;
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         }
         const int page_base = p.paged ? info.kv_base : 0;
         const int tok_base = p.paged ? 0 : info.kv_base;
-        for (; page >= 0 && ok; page = walk.next()) {
-          ++pg_total;
+        // K (and V) of one page into the next ring slots (lane 0)
+        auto load_page = [&](int page) {
           const int phys = p.paged ? __ldg(p.kv_indices + page_base + page) : 0;
           const int tok_k = tok_base + (page << 7);
           const size_t tile = static_cast<size_t>(phys) * p.Hkv + info.g;
@@ -904,7 +957,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           if constexpr (Cfg::kKConvert) {
             const int s = raw_seq % NRAW;
             ok = mbar_wait(&sm.raw_empty[s], ((raw_seq / NRAW) & 1) ^ 1, abort_flag);
-            if (!ok) break;
+            if (!ok) return;
             ++raw_seq;
             mbar_expect_tx(&sm.raw_full[s], 8192 + 1024);
             bulk_load(sm.raw[s], p.k_raw + tile * 8192, 8192, &sm.raw_full[s]);
@@ -914,7 +967,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             MSA_TBEGIN
             ok = mbar_wait(&sm.k_empty[s], ((k_seq / NK) & 1) ^ 1, abort_flag);
             MSA_TEND(13)
-            if (!ok) break;
+            if (!ok) return;
             ++k_seq;
             mbar_expect_tx(&sm.k_full[s], Cfg::kKBytes);
             if constexpr (Cfg::kKDirectFp8) {
@@ -930,12 +983,12 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
               tma_load_3d(sm.k[s] + kHalfBytes, &tmap_k, &sm.k_full[s], 64, info.g, tok_k);
             }
           }
-          if (!p.do_pv) continue;
+          if (!p.do_pv) return;
           // ---- V ----
           if constexpr (Cfg::kVConvert) {
             const int s = raw_seq % NRAW;
             ok = mbar_wait(&sm.raw_empty[s], ((raw_seq / NRAW) & 1) ^ 1, abort_flag);
-            if (!ok) break;
+            if (!ok) return;
             ++raw_seq;
             if constexpr (KVMODE == KV_FP8) {
               mbar_expect_tx(&sm.raw_full[s], 16384);
@@ -951,7 +1004,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           } else {
             const int s = v_seq % NV;
             ok = mbar_wait(&sm.v_empty[s], ((v_seq / NV) & 1) ^ 1, abort_flag);
-            if (!ok) break;
+            if (!ok) return;
             ++v_seq;
             mbar_expect_tx(&sm.v_full[s], kTileBytes);
             if (p.paged) {
@@ -962,6 +1015,24 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
               tma_load_3d(sm.v[s] + kHalfBytes, &tmap_v, &sm.v_full[s], 64, info.g, tok_k);
             }
           }
+        };
+        int issued = 0;
+        for (; page >= 0 && ok; page = walk.next()) {
+          ++pg_total;
+          if (lane == 0) load_page(page);
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          // three pages of this item are on their way: time to prepare the next item
+          if (++issued == 3 && next_pending && ok) {
+            MSA_TBEGIN
+            build_bitmap(next_item, j + 1);
+            MSA_TEND(11)
+            next_pending = false;
+          }
+        }
+        if (next_pending && ok) {
+          MSA_TBEGIN
+          build_bitmap(next_item, j + 1);
+          MSA_TEND(11)
         }
       }
       MSA_TFLUSH(lane == 0, 11, 14)
