@@ -619,23 +619,30 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       const bool via_tma = Cfg::kStageOut && __all_sync(0xffffffffu, pend.row_valid);
       uint8_t* stage = sm.o_stage[Cfg::kStageOut ? warp : 0];
       const int row32 = r & 31;
-      uint32_t rg[32];
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {   // not unrolled: once per item, and the kernel's code should stay cache-sized
-        if (pend.n_iter > 0) {
-          tmem_ld32(o_addr + c * 32, rg);
-          tmem_ld_wait();
-        } else {
+      // the whole O row at once (the registers of the S row are free here): one TMEM round trip, not four
+      uint32_t rg[128];
+      if (pend.n_iter > 0) {
+        tmem_ld32p(o_addr, rg);
+        tmem_ld32p(o_addr + 32, rg + 32);
+        tmem_ld32p(o_addr + 64, rg + 64);
+        tmem_ld32p(o_addr + 96, rg + 96);
+        tmem_ld_wait();
+      } else {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) rg[e] = 0u;
-        }
+        for (int e = 0; e < 128; ++e) rg[e] = 0u;
+      }
+      // O has been read: the next item's first PV may overwrite it (it waits for my next P anyway)
+      tc_fence_before();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
         uint4 o[4];
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
-          o[v].x = pack_bf16x2(__uint_as_float(rg[v * 8 + 0]) * inv, __uint_as_float(rg[v * 8 + 1]) * inv);
-          o[v].y = pack_bf16x2(__uint_as_float(rg[v * 8 + 2]) * inv, __uint_as_float(rg[v * 8 + 3]) * inv);
-          o[v].z = pack_bf16x2(__uint_as_float(rg[v * 8 + 4]) * inv, __uint_as_float(rg[v * 8 + 5]) * inv);
-          o[v].w = pack_bf16x2(__uint_as_float(rg[v * 8 + 6]) * inv, __uint_as_float(rg[v * 8 + 7]) * inv);
+          const int e = c * 32 + v * 8;
+          o[v].x = pack_bf16x2(__uint_as_float(rg[e + 0]) * inv, __uint_as_float(rg[e + 1]) * inv);
+          o[v].y = pack_bf16x2(__uint_as_float(rg[e + 2]) * inv, __uint_as_float(rg[e + 3]) * inv);
+          o[v].z = pack_bf16x2(__uint_as_float(rg[e + 4]) * inv, __uint_as_float(rg[e + 5]) * inv);
+          o[v].w = pack_bf16x2(__uint_as_float(rg[e + 6]) * inv, __uint_as_float(rg[e + 7]) * inv);
         }
         if (via_tma) {
           if (lane == 0) tma_store_wait_read();   // the previous piece has left the staging buffer
@@ -662,8 +669,6 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                             : -INFINITY;
         p.lse[static_cast<size_t>(pend.tok) * p.Hq + pend.h] = v;
       }
-      // O has been read: the next item's first PV may overwrite it (it waits for my next P anyway)
-      tc_fence_before();
     };
 
     // The loop starts one (virtual) item early: its first pass has nothing to compute and only prepares the
@@ -816,17 +821,19 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       pend.n_iter = n_iter;
       pend.row_valid = row_valid;
       }
-      // ---- hand the tensor core the next item's Q before draining this item's O -------
+      // ---- drain this item's O, then prepare the next item.  The next Q was requested only when this item's
+      // last QK completed and is still on its way from HBM: the drain fills that wait, and the Q rewrite that
+      // follows finds its tile in shared memory.
       const int next_item = item + item_step;
+      MSA_TBEGIN
+      epilogue();
+      if (r == 0 && t == 0) { MSA_TRACE(10, it_total, clock64()) }
+      MSA_TEND(10)
       MSA_TBEGIN
       if (r == 0 && t == 0) { MSA_TRACE(8, it_total, clock64()) }
       if (next_item < p.n_items && ok) setup(next_item, j + 1);
       if (r == 0 && t == 0) { MSA_TRACE(9, it_total, clock64()) }
       MSA_TEND(2)
-      MSA_TBEGIN
-      epilogue();
-      if (r == 0 && t == 0) { MSA_TRACE(10, it_total, clock64()) }
-      MSA_TEND(10)
     }
     if (lane == 0) tma_store_wait_all();   // this warp's output pieces have left shared memory and are written
     MSA_TFLUSH(tid == 0, 0, 3)
