@@ -68,6 +68,8 @@ typedef struct msa_plan_desc {
   int32_t kv_block_num;     /* page-list length of a sparse call (> 0), else <= 0 */
   int32_t num_kv_splits;    /* > 0 forces the decode split count, else chosen for whole waves of CTAs */
   int32_t num_sms;          /* SMs the decode split choice may assume (usable_SM_count), <= 0 = 148 */
+  int32_t tile_rows;        /* query rows per work entry: 0 or 128, or 256 for the paired-tile score-only pass
+                               (msa_fmha_args.tile_rows) */
 } msa_plan_desc;
 
 /* Sizes of the arrays msa_plan fills: query tiles, total query tokens, total page-table slots. */
@@ -165,6 +167,10 @@ typedef struct msa_fmha_args {
   int32_t max_ctas;       /* > 0 caps the persistent grid (the reference's usable_SM_count); 0 = one CTA per SM */
   int32_t qk_dim;         /* 0 or 128: all of the head dimension; 64: the score-only pass (out = NULL) uses only the
                              first 64 elements of q and k (a 64-wide proxy zero-padded to 128 costs half) */
+  int32_t tile_rows;      /* 0 or 128: `work` holds 128-row tiles.  256: `work` holds 256-row tiles (msa_plan_desc.tile_rows
+                             = 256) and each CTA step runs the two 128-row halves side by side against one K page --
+                             only for the score-only pass (out = NULL, no page lists) with an odd number of query
+                             heads per KV head, where there is no second head to pair with (a single proxy head) */
   const uint8_t* tile_uniform;   /* optional, uint8 [n_work, list_heads] from msa_list_uniformity: non-zero where all
                                     rows of a query tile carry the same page list (the tile's page set is then taken
                                     from one row instead of 128); NULL = no tile is assumed uniform */

@@ -41,7 +41,7 @@ class FmhaArgs(Structure):
         ("kv_dtype", c_int32), ("paged", c_int32), ("causal", c_int32),
         ("sm_scale", c_float), ("qk_scale", c_float), ("v_scale", c_float),
         ("status", c_void_p), ("max_ctas", c_int32), ("qk_dim", c_int32),
-        ("tile_uniform", c_void_p), ("max_score_tile_stride", c_int64), ("max_score_head_stride", c_int64),
+        ("tile_rows", c_int32), ("tile_uniform", c_void_p), ("max_score_tile_stride", c_int64), ("max_score_head_stride", c_int64),
     ]
 
 
@@ -72,7 +72,7 @@ class PlanDesc(Structure):
     _fields_ = [
         ("batch", c_int32), ("qo_lens", c_void_p), ("kv_lens", c_void_p), ("qo_offset", c_void_p),
         ("causal", c_int32), ("paged", c_int32), ("num_qo_heads", c_int32), ("num_kv_heads", c_int32),
-        ("kv_block_num", c_int32), ("num_kv_splits", c_int32), ("num_sms", c_int32),
+        ("kv_block_num", c_int32), ("num_kv_splits", c_int32), ("num_sms", c_int32), ("tile_rows", c_int32),
     ]
 
 

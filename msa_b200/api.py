@@ -62,7 +62,8 @@ def _np_ptr(a: Optional[np.ndarray]):
 
 
 def _host_plan(qo_lens, kv_lens, qo_offset, causal: bool, paged: bool, num_qo_heads: int = 1, num_kv_heads: int = 1,
-               kv_block_num: int = -1, num_kv_splits: int = -1, num_sms: int = 0, decode: bool = False):
+               kv_block_num: int = -1, num_kv_splits: int = -1, num_sms: int = 0, decode: bool = False,
+               tile_rows: int = 128):
     """Runs ``msa_plan`` (the host planner of libmsa_b200.so, standing in for
     csrc/fmha_sm100_plan.cu:18-35 and csrc/include/plan.cuh:899-1054 of the reference) and
     returns host arrays: ``(work[n_work, 8], kv_page_indptr[B + 1], token_request, token_pos, num_splits)``;
@@ -76,6 +77,7 @@ def _host_plan(qo_lens, kv_lens, qo_offset, causal: bool, paged: bool, num_qo_he
     d.causal, d.paged = int(bool(causal)), int(bool(paged))
     d.num_qo_heads, d.num_kv_heads = int(num_qo_heads), int(num_kv_heads)
     d.kv_block_num, d.num_kv_splits, d.num_sms = int(kv_block_num), int(num_kv_splits or -1), int(num_sms)
+    d.tile_rows = int(tile_rows)
     n_work, total_q, total_pages = ctypes.c_int32(0), ctypes.c_int64(0), ctypes.c_int64(0)
     check(lib.msa_plan_sizes(ctypes.byref(d), ctypes.byref(n_work), ctypes.byref(total_q), ctypes.byref(total_pages)),
           "msa_plan_sizes")
@@ -183,6 +185,11 @@ def _fmha_sm100_plan(
     plan["qo_offset"] = _i32(off, device)
     plan["work"] = torch.from_numpy(work).to(device).contiguous()
     plan["n_work"] = int(work.shape[0])
+    if output_maxscore and not sparse and (num_qo_heads // num_kv_heads) % 2 == 1:
+        # score-only calls over an odd number of heads per KV head (a single proxy head) pair two query tiles
+        # of one head on a CTA instead of two heads: 256-row work entries
+        work2 = _host_plan(qo_lens, kv_lens, off, causal, page_size > 0, num_qo_heads, num_kv_heads, tile_rows=256)[0]
+        plan["work_pair"] = torch.from_numpy(work2).to(device).contiguous()
     plan["status"] = torch.zeros(1, dtype=torch.int32, device=device)
     plan["use_decode_kernel"] = bool(use_decode)
     plan["pack_factor"] = 1
@@ -290,14 +297,16 @@ def _run_prefill(q, k, v, plan, kv_indices, kv_block_indexes, qo_offset_t, out, 
     a.qk_dim = int(qk_dim)
     a.q, a.k, a.v = _ptr(q), _ptr(k), _ptr(v)
     a.out, a.lse, a.max_score = _ptr(out), _ptr(lse), _ptr(max_score)
-    work = plan["work"]
+    pair = out is None and kv_block_indexes is None and "work_pair" in plan
+    work = plan["work_pair"] if pair else plan["work"]
     if qo_offset_t is not plan["qo_offset"]:
         # runtime causal-offset override: patch column 5 of a copy of the work list
         work = work.clone()
         work[:, 5] = qo_offset_t.to(torch.int32)[work[:, 0].long()]
     if bool(is_paged) != (plan["page_size"] > 0):
         raise MsaError("the plan and the call disagree on paged vs ragged K/V (pass page_size to fmha_sm100_plan)")
-    a.work, a.n_work = _ptr(work), plan["n_work"]
+    a.work, a.n_work = _ptr(work), int(work.shape[0])
+    a.tile_rows = 256 if pair else 128
     a.kv_indices = _ptr(kv_indices)
     a.kv_block_indexes = _ptr(kv_block_indexes)
     a.k_scale_128x4, a.v_scale_128x4 = _ptr(k_sf), _ptr(v_sf)
@@ -307,11 +316,11 @@ def _run_prefill(q, k, v, plan, kv_indices, kv_block_indexes, qo_offset_t, out, 
     a.topk = kv_block_indexes.shape[2] if kv_block_indexes is not None else 0
     a.list_heads = kv_block_indexes.shape[1] if kv_block_indexes is not None else 0
     flags = None
-    if kv_block_indexes is not None and plan["n_work"] > 0:
+    if kv_block_indexes is not None and a.n_work > 0:
         # which query tiles carry one list for all their rows (pages selected per query block): a short device
         # pass over the lists, then the attention kernel takes such a tile's page set from a single row
-        flags = torch.empty(plan["n_work"] * a.list_heads, dtype=torch.uint8, device=q.device)
-        check(lib.msa_list_uniformity(_ptr(work), plan["n_work"], _ptr(kv_block_indexes), a.list_heads, a.topk,
+        flags = torch.empty(a.n_work * a.list_heads, dtype=torch.uint8, device=q.device)
+        check(lib.msa_list_uniformity(_ptr(work), a.n_work, _ptr(kv_block_indexes), a.list_heads, a.topk,
                                       _ptr(flags), _stream()), "msa_list_uniformity")
     a.tile_uniform = _ptr(flags)
     a.max_k_tiles = max_score.shape[1] if max_score is not None else 0

@@ -85,20 +85,20 @@ int make_paged_e4m3_map(void* tensor_map, const void* kv, int64_t pages, int hkv
 static long long* g_timing_buffer = nullptr;
 void set_timing_buffer(void* ptr) { g_timing_buffer = static_cast<long long*>(ptr); }
 
-template <int NT, int KVMODE>
-static int launch_fmha(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
+template <int NT, int KVMODE, bool SCORE, int LISTS>
+static int launch_fmha_mode(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
                        const FmhaParams& p, int max_ctas, cudaStream_t st) {
   using Cfg = FmhaCfg<NT, KVMODE>;
   static DeviceSetup setup;
   int num_sms = 0;
   constexpr int smem = fmha_smem_bytes<NT, KVMODE>();
   const int rc = setup.ensure(&num_sms, [] {
-    cudaError_t e = cudaFuncSetAttribute(fmha_fwd_kernel<NT, KVMODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(fmha_fwd_kernel<NT, KVMODE, SCORE, LISTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
     if (Cfg::kRebalance) {
       // the in-kernel register hand-over only balances if the CTA starts with exactly kRegsLaunch per thread
       cudaFuncAttributes fa;
-      e = cudaFuncGetAttributes(&fa, fmha_fwd_kernel<NT, KVMODE>);
+      e = cudaFuncGetAttributes(&fa, fmha_fwd_kernel<NT, KVMODE, SCORE, LISTS>);
       if (e != cudaSuccess) return static_cast<int>(e);
       if (fa.numRegs != Cfg::kRegsLaunch) return static_cast<int>(MSA_ERR_UNSUPPORTED);
     }
@@ -108,8 +108,16 @@ static int launch_fmha(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
   // persistent: one CTA per SM walks the item list with stride gridDim.x; max_ctas > 0 caps the grid
   int ctas = p.n_items < num_sms ? p.n_items : num_sms;
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
-  fmha_fwd_kernel<NT, KVMODE><<<static_cast<unsigned>(ctas), Cfg::kThreads, smem, st>>>(mq, mk, mv, mo, p);
+  fmha_fwd_kernel<NT, KVMODE, SCORE, LISTS><<<static_cast<unsigned>(ctas), Cfg::kThreads, smem, st>>>(mq, mk, mv, mo, p);
   return static_cast<int>(cudaGetLastError());
+}
+
+template <int NT, int KVMODE>
+static int launch_fmha(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
+                       const FmhaParams& p, int max_ctas, cudaStream_t st) {
+  if (!p.do_pv) return launch_fmha_mode<NT, KVMODE, true, 0>(mq, mk, mv, mo, p, max_ctas, st);
+  return p.sparse ? launch_fmha_mode<NT, KVMODE, false, 1>(mq, mk, mv, mo, p, max_ctas, st)
+                  : launch_fmha_mode<NT, KVMODE, false, 0>(mq, mk, mv, mo, p, max_ctas, st);
 }
 
 int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
@@ -168,8 +176,18 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
   p.timing = g_timing_buffer;
 
   // two query heads share one K/V stream when they share a KV head and a page list
-  const int nt = (p.hr % 2 == 0 && (!sparse || a->list_heads == a->num_kv_heads)) ? 2 : 1;
+  int nt = (p.hr % 2 == 0 && (!sparse || a->list_heads == a->num_kv_heads)) ? 2 : 1;
+  p.pair_tiles = 0;
   p.n_head_groups = p.Hq / nt;
+  if (a->tile_rows == 256) {
+    // no second head to pair with: the two tiles of a CTA are the halves of a 256-row work entry of one head
+    if (nt != 1 || sparse || a->out != nullptr) return MSA_ERR_UNSUPPORTED;
+    nt = 2;
+    p.pair_tiles = 1;
+    p.n_head_groups = p.Hq;
+  } else if (a->tile_rows != 0 && a->tile_rows != 128) {
+    return MSA_ERR_INVALID;
+  }
   const long long n_items = static_cast<long long>(p.n_work) * p.n_head_groups;
   if (n_items > 0x7fffffffLL) return MSA_ERR_TOO_LARGE;
   p.n_items = static_cast<int>(n_items);

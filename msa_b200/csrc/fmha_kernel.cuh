@@ -79,6 +79,8 @@ struct FmhaParams {
   int Hq, Hkv, hr, topk, list_heads, total_q, max_k_tiles, n_work, n_head_groups, n_items;
   int causal, paged, sparse, do_pv, do_maxscore;
   int half_dim;                  // score-only pass over the first 64 of the 128 head-dim elements
+  int pair_tiles;                // score-only pass: the two tiles of a CTA are the 128-row halves of one 256-row work
+                                 // entry of ONE head (instead of two heads of one 128-row entry)
   float scale_log2;              // softmax scale * log2(e) * (q_scale * k_scale [* k_global])
   float out_scale;               // v_scale * o_scale [* v_global]
   int* status;
@@ -95,6 +97,9 @@ struct FmhaCfg {
   static constexpr int kKBytes = kKDirectFp8 ? kHalfBytes : kTileBytes;
   static constexpr int kKStages = 2;
   static constexpr int kVStages = 2;
+  // Score-only pass (no V, nothing converted): the V tiles' shared memory serves as further K stages, because
+  // with one K page per step and no P.V to hide behind, the depth of the K ring is what covers the load latency.
+  static constexpr int kKStagesScore = kKConvert ? kKStages : kKStages + kVStages * kTileBytes / kKBytes;
   static constexpr int kRawStages = kQuant ? 2 : 0;
   static constexpr int kRawBytes = KVMODE == KV_NVFP4 ? 10240 : 16384;
   static constexpr int kSoftmaxWarps = 4 * NT;
@@ -135,7 +140,7 @@ struct __align__(1024) FmhaSmem {
   // rows that lie num_qo_heads * 256 bytes apart
   alignas(1024) uint8_t o_stage[Cfg::kStageOut ? Cfg::kSoftmaxWarps : 1][Cfg::kStageOut ? 2048 : 16];
   uint64_t q_full, q_ready, q_empty;
-  uint64_t k_full[Cfg::kKStages], k_empty[Cfg::kKStages];
+  uint64_t k_full[Cfg::kKStagesScore], k_empty[Cfg::kKStagesScore];
   uint64_t v_full[Cfg::kVStages], v_empty[Cfg::kVStages];
   uint64_t raw_full[Cfg::kRawStages > 0 ? Cfg::kRawStages : 1], raw_empty[Cfg::kRawStages > 0 ? Cfg::kRawStages : 1];
   uint64_t s_full[NT], p_full[NT], o_final[NT];
@@ -205,7 +210,7 @@ __device__ __forceinline__ ItemInfo decode_item(const FmhaParams& p, int item, i
   it.tok0 = w.y;
   it.rows = w.z;
   it.qloc0 = w.w;
-  it.h0 = hg * nt;
+  it.h0 = p.pair_tiles ? hg : hg * nt;
   it.g = it.h0 / p.hr;
   it.kv_len = w2.x;
   it.qo_off = w2.y;
@@ -303,10 +308,11 @@ __device__ __forceinline__ void e4m3x2_to_f32x2(uint32_t v, float& a, float& b) 
 // MMA issue with everything but the dynamic shared-memory base known at compile time (tile, ring stage,
 // k-step): operands then live on the uniform datapath instead of being moved there per instruction.
 // TMEM addresses are absolute: the kernel owns all 512 columns, so the allocation starts at column 0.
-template <class Cfg, class Smem, int T, int S>
-__device__ __forceinline__ void issue_qk_static(Smem& sm, uint32_t d_off = 0, bool half_dim = false) {
+// S_T (+ d_off columns) = Q_T K^T with the K tile at shared-memory address k_saddr
+template <class Cfg, class Smem, int T>
+__device__ __forceinline__ void issue_qk_at(Smem& sm, uint32_t k_saddr, uint32_t d_off = 0, bool half_dim = false) {
   constexpr uint32_t desc_hi = smem_desc_hi(1024);
-  const uint32_t qa = smem_desc_lo(smem_u32(sm.q[T]), 16), ka = smem_desc_lo(smem_u32(sm.k[S]), 16);
+  const uint32_t qa = smem_desc_lo(smem_u32(sm.q[T]), 16), ka = smem_desc_lo(k_saddr, 16);
   const uint32_t d = T * 128 + d_off;
   if constexpr (Cfg::kKDirectFp8) {
     // S = Q_hi K^T + Q_lo K^T: 2 x 4 steps of 32 contraction bytes inside the 128-byte swizzle row
@@ -350,6 +356,11 @@ __device__ __forceinline__ void issue_pv_static(Smem& sm, uint32_t accumulate) {
 #pragma unroll
   for (int ks = 1; ks < 8; ++ks) umma_ts_lohi(d, a + ks * 8, va + ks * 128, desc_hi, idesc, 1u);
 }
+// same with the ring stage known at the call site, so that the addresses are constants plus the buffer base
+template <class Cfg, class Smem, int T, int S>
+__device__ __forceinline__ void issue_qk_static(Smem& sm, uint32_t d_off = 0, bool half_dim = false) {
+  issue_qk_at<Cfg, Smem, T>(sm, smem_u32(sm.k[S]), d_off, half_dim);
+}
 template <class Cfg, class Smem, int T>
 __device__ __forceinline__ void issue_qk_stage(Smem& sm, int stage, uint32_t d_off = 0, bool half_dim = false) {
   if (stage == 0) issue_qk_static<Cfg, Smem, T, 0>(sm, d_off, half_dim);
@@ -362,14 +373,22 @@ __device__ __forceinline__ void issue_pv_stage(Smem& sm, int stage, uint32_t acc
   else issue_pv_static<Cfg, Smem, T, 1>(sm, accumulate);
 }
 
-template <int NT, int KVMODE>
+// SCORE: the score-only pass (per-page max of Q K^T, no softmax, no V) as a kernel of its own, so that neither
+// variant carries the other's code
+// LISTS: 0 = no page lists (dense walk only), 1 = decided at run time by p.sparse (the variant page-list calls
+// use).  The dense specialisation is measurably faster than the generic code on dense calls, while the
+// generic code is the faster one on page-list calls, so each kind of call gets its own instantiation.
+template <int NT, int KVMODE, bool SCORE, int LISTS>
 __global__ void __launch_bounds__(FmhaCfg<NT, KVMODE>::kThreads, 1)
 fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
                 const FmhaParams p) {
   using Cfg = FmhaCfg<NT, KVMODE>;
   using Smem = FmhaSmem<NT, KVMODE>;
-  constexpr int NK = Cfg::kKStages, NV = Cfg::kVStages;
+  constexpr int NK = Cfg::kKStages, NV = Cfg::kVStages, NKS = Cfg::kKStagesScore;
+  constexpr bool kDoPv = !SCORE;
+  const bool sparse = LISTS != 0 && p.sparse != 0;
+  const bool pair_tiles = SCORE && p.pair_tiles != 0;
   constexpr int NRAW = Cfg::kRawStages > 0 ? Cfg::kRawStages : 1;
   extern __shared__ uint8_t smem_raw[];
   Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -383,27 +402,27 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   // ---- one-time setup ---------------------------------------------------------
   if (tid == 0) {
     mbar_init(&sm.q_full, 1);
-    mbar_init(&sm.q_ready, 128 * NT);
+    mbar_init(&sm.q_ready, 4 * NT);              // one arrival per softmax warp
     mbar_init(&sm.q_empty, 1);
-    for (int s = 0; s < NK; ++s) {
-      mbar_init(&sm.k_full[s], Cfg::kKConvert ? Cfg::kCvtThreads : 1);
+    for (int s = 0; s < NKS; ++s) {
+      mbar_init(&sm.k_full[s], Cfg::kKConvert ? Cfg::kCvtThreads / 32 : 1);
       mbar_init(&sm.k_empty[s], 1);
     }
     for (int s = 0; s < NV; ++s) {
-      mbar_init(&sm.v_full[s], Cfg::kVConvert ? Cfg::kCvtThreads : 1);
+      mbar_init(&sm.v_full[s], Cfg::kVConvert ? Cfg::kCvtThreads / 32 : 1);
       mbar_init(&sm.v_empty[s], 1);
     }
     for (int s = 0; s < NRAW; ++s) {
       mbar_init(&sm.raw_full[s], 1);
-      mbar_init(&sm.raw_empty[s], Cfg::kCvtThreads);
+      mbar_init(&sm.raw_empty[s], Cfg::kCvtThreads / 32);
     }
     for (int t = 0; t < NT; ++t) {
       mbar_init(&sm.s_full[t], 1);
-      mbar_init(&sm.p_full[t], 128);
+      mbar_init(&sm.p_full[t], 128);              // every softmax thread arrives (measured faster than one per warp)
       mbar_init(&sm.o_final[t], 1);
       for (int b2 = 0; b2 < 2; ++b2) {
         mbar_init(&sm.sc_full[t][b2], 1);
-        mbar_init(&sm.sc_free[t][b2], 128);
+        mbar_init(&sm.sc_free[t][b2], 4);
       }
     }
     for (int b = 0; b < 2; ++b) {
@@ -430,7 +449,25 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   // the MMA warp addresses TMEM absolutely (all 512 columns are ours, so the base can only be column 0)
   if (tmem != 0 && tid == 0) sm.abort = 1;
   __syncthreads();
-  const int item0 = (sm.abort == 0) ? blockIdx.x : p.n_items, item_step = gridDim.x;
+  // K ring in effect: deeper in the score-only pass, where stages beyond the first NK live in the V tiles' memory
+  constexpr int nk_ring = SCORE ? NKS : NK;
+  auto k_stage_ptr = [&](int st) -> uint8_t* {
+    return st < NK ? sm.k[st] : &sm.v[0][0] + static_cast<size_t>(st - NK) * Cfg::kKBytes;
+  };
+  // The j-th item of this CTA, or -1 past the end.  The list is ordered heaviest first and the CTAs walk it in
+  // rounds of gridDim.x items, forwards in even rounds and backwards in odd ones (a snake), so that the CTA
+  // that drew the heaviest item of one round draws the lightest of the next.
+  const int n_items_eff = (sm.abort == 0) ? p.n_items : 0;
+  auto item_of = [&](int j) {
+    const int base = j * static_cast<int>(gridDim.x);
+#ifdef MSA_NO_SNAKE
+    const int idx = base + static_cast<int>(blockIdx.x);
+#else
+    const int idx = (j & 1) ? base + static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)
+                            : base + static_cast<int>(blockIdx.x);
+#endif
+    return (base < n_items_eff && idx < n_items_eff) ? idx : -1;
+  };
 
   if (warp < Cfg::kSoftmaxWarps) {
     // =========================================================================
@@ -477,14 +514,15 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     // prepares item `item` (index j in this CTA's sequence): row visibility, list cursor, Q rewrite
     auto setup = [&](int item, int j) {
       nx.bm = j & 1;
-      if (p.sparse) {
+      if (sparse) {
         // the producer published the item's work record (and a uniform tile's list cursor) with the bitmap
         ok = ok && mbar_wait(&sm.bm_full[nx.bm], (j >> 1) & 1, abort_flag);
         nx.info = decode_item(p, item, NT, sm.item_work[nx.bm][0], sm.item_work[nx.bm][1]);
       } else {
         nx.info = load_item(p, item, NT);
       }
-      nx.row_valid = r < nx.info.rows;
+      const int r_tile = pair_tiles ? t * 128 + r : r;   // my row within the work entry
+      nx.row_valid = r_tile < nx.info.rows;
       nx.limit_base = -1;
       nx.list = nullptr;
       nx.cur = -1;
@@ -493,9 +531,9 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       nx.sl2 = p.scale_log2;
       if (nx.row_valid) {
         nx.limit_base = nx.info.kv_len - 1;
-        if (p.causal) nx.limit_base = min(nx.limit_base, nx.info.qloc0 + r + nx.info.qo_off);
+        if (p.causal) nx.limit_base = min(nx.limit_base, nx.info.qloc0 + r_tile + nx.info.qo_off);
       }
-      if (p.sparse && nx.row_valid) {
+      if (sparse && nx.row_valid) {
         const int lh = (p.list_heads == p.Hkv) ? nx.info.g : (nx.info.h0 + t);
         nx.list = p.kv_block_indexes + (static_cast<size_t>(nx.info.tok0 + r) * p.list_heads + lh) * p.topk;
         if (sm.item_uniform[nx.bm]) {
@@ -517,7 +555,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           nx.prev_page = prev_page;
         }
       }
-      nx.walk.init(p.sparse, sm.bitmap[nx.bm], nx.info.walk_n);
+      nx.walk.init(sparse, sm.bitmap[nx.bm], nx.info.walk_n);
       nx.first_page = ok ? nx.walk.next() : -1;
       if (nx.first_page >= 0) {
         if constexpr (Cfg::kQConvert) {
@@ -590,7 +628,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
             fence_proxy_async();
           }
-          mbar_arrive(&sm.q_ready);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sm.q_ready);
         }
         ++n_q;
       }
@@ -601,7 +640,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     auto epilogue = [&]() {
       if (!pend.valid) return;
       pend.valid = false;
-      if (!p.do_pv) return;
+      if (!kDoPv) return;
       if (pend.n_iter > 0) {
         ok = ok && mbar_wait(&sm.o_final[t], n_fin & 1, abort_flag);
         ++n_fin;
@@ -673,13 +712,13 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 
     // The loop starts one (virtual) item early: its first pass has nothing to compute and only prepares the
     // CTA's first item, so that setup -- a long unrolled piece of code -- has a single call site.
-    int j = -1;
-    for (int item = item0 - item_step; item < p.n_items && ok; item += item_step, ++j) {
+    for (int j = -1; ok; ++j) {
+      if (j >= 0 && item_of(j) < 0) break;
       if (j >= 0) {
       // ---- main loop of the item prepared in nx -------------------------------
       const ItemInfo info = nx.info;
-      const int h = info.h0 + t;
-      const int tok = info.tok0 + r;
+      const int h = pair_tiles ? info.h0 : info.h0 + t;
+      const int tok = info.tok0 + (pair_tiles ? t * 128 + r : r);
       const bool row_valid = nx.row_valid;
       const int limit_base = nx.limit_base;
       const int* list = nx.list;
@@ -694,7 +733,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       for (int page = nx.first_page; page >= 0 && ok; page = walk.next(), ++n_iter, ++it_total) {
         // visibility of this page for my row
         int limit = limit_base - (page << 7);
-        if (p.sparse) {
+        if (sparse) {
           // the walk descends, so does the cursor; the entry below the current one is fetched one step
           // ahead so that its load latency never sits in front of a softmax step
           while (cur >= 0 && cur_page > page) {
@@ -707,17 +746,17 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const bool full_vis = __all_sync(0xffffffffu, limit >= 127);
 
         // score-only pass: the S tiles alternate between columns [t*128, +128) and the O columns 256 further
-        const int sb = p.do_pv ? 0 : static_cast<int>(it_total & 1);
+        const int sb = kDoPv ? 0 : static_cast<int>(it_total & 1);
         MSA_TBEGIN
-        ok = p.do_pv ? mbar_wait(&sm.s_full[t], it_total & 1, abort_flag)
+        ok = kDoPv ? mbar_wait(&sm.s_full[t], it_total & 1, abort_flag)
                      : mbar_wait(&sm.sc_full[t][sb], (it_total >> 1) & 1, abort_flag);
         MSA_TEND(0)
         if (!ok) break;
         tc_fence_after();
         if (releaser) {
-          mbar_arrive(&sm.k_empty[k_rel % NK]);
+          mbar_arrive(&sm.k_empty[k_rel % nk_ring]);
           ++k_rel;
-          if (p.do_pv && n_iter > 0) {
+          if (kDoPv && n_iter > 0) {
             mbar_arrive(&sm.v_empty[v_rel % NV]);
             ++v_rel;
           }
@@ -733,10 +772,11 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         tmem_ld32p(s_cur + 64, sr + 64);
         tmem_ld32p(s_cur + 96, sr + 96);
         tmem_ld_wait();
-        if (!p.do_pv) {
+        if (!kDoPv) {
           // score-only pass: S is in registers, the MMA warp may overwrite this buffer
           tc_fence_before();
-          mbar_arrive(&sm.sc_free[t][sb]);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sm.sc_free[t][sb]);
         }
         if (!full_vis) {
 #pragma unroll
@@ -754,7 +794,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         if (p.do_maxscore && row_valid)
           __stwt(p.max_score + h * p.ms_head + page * p.ms_tile + tok, tmax * ms_scale);
 
-        if (p.do_pv) {
+        if (kDoPv) {
           const float m_new = fmaxf(m_used, tmax);
           const bool first = (m_used == -INFINITY);
           const bool need = !first && ((m_new - m_used) * sl2 > kRescaleThreshold);
@@ -808,7 +848,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         MSA_TEND(1)
       }
       // this item's bitmap is no longer needed by my warp
-      if (p.sparse) {
+      if (sparse) {
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.bm_empty[my_bm]);
       }
@@ -824,14 +864,14 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // ---- drain this item's O, then prepare the next item.  The next Q was requested only when this item's
       // last QK completed and is still on its way from HBM: the drain fills that wait, and the Q rewrite that
       // follows finds its tile in shared memory.
-      const int next_item = item + item_step;
+      const int next_item = item_of(j + 1);
       MSA_TBEGIN
       epilogue();
       if (r == 0 && t == 0) { MSA_TRACE(10, it_total, clock64()) }
       MSA_TEND(10)
       MSA_TBEGIN
       if (r == 0 && t == 0) { MSA_TRACE(8, it_total, clock64()) }
-      if (next_item < p.n_items && ok) setup(next_item, j + 1);
+      if (next_item >= 0 && ok) setup(next_item, j + 1);
       if (r == 0 && t == 0) { MSA_TRACE(9, it_total, clock64()) }
       MSA_TEND(2)
     }
@@ -921,19 +961,20 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         if (lane == 0) mbar_arrive(&sm.bm_full[b]);
       };
       MSA_TBEGIN
-      if (p.sparse && item0 < p.n_items) build_bitmap(item0, 0);
+      if (sparse && item_of(0) >= 0) build_bitmap(item_of(0), 0);
       MSA_TEND(11)
-      int j = 0;
-      for (int item = item0; item < p.n_items && ok; item += item_step, ++j) {
+      for (int j = 0; ok; ++j) {
+        const int item = item_of(j);
+        if (item < 0) break;
         if (lane == 0) { MSA_TRACE(11, pg_total, clock64()) }
         const int b = j & 1;
-        const ItemInfo info = p.sparse ? decode_item(p, item, NT, sm.item_work[b][0], sm.item_work[b][1])
+        const ItemInfo info = sparse ? decode_item(p, item, NT, sm.item_work[b][0], sm.item_work[b][1])
                                        : load_item(p, item, NT);
-        const int next_item = item + item_step;
-        bool next_pending = p.sparse && next_item < p.n_items;
+        const int next_item = item_of(j + 1);
+        bool next_pending = sparse && next_item >= 0;
         if (lane == 0) { MSA_TRACE(12, pg_total, clock64()) }
         PageWalk walk;
-        walk.init(p.sparse, sm.bitmap[b], info.walk_n);
+        walk.init(sparse, sm.bitmap[b], info.walk_n);
         int page = walk.next();
         if (page >= 0) {
           // Q of this item: the tile buffer is free once the previous item's last QK has completed
@@ -945,8 +986,9 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
               MSA_TRACE(13, pg_total, clock64())
               mbar_expect_tx(&sm.q_full, NT * kTileBytes);
               for (int t = 0; t < NT; ++t) {
-                tma_load_3d(sm.q[t], &tmap_q, &sm.q_full, 0, info.h0 + t, info.tok0);
-                tma_load_3d(sm.q[t] + kHalfBytes, &tmap_q, &sm.q_full, 64, info.h0 + t, info.tok0);
+                const int qh = pair_tiles ? info.h0 : info.h0 + t, qt = pair_tiles ? info.tok0 + t * 128 : info.tok0;
+                tma_load_3d(sm.q[t], &tmap_q, &sm.q_full, 0, qh, qt);
+                tma_load_3d(sm.q[t] + kHalfBytes, &tmap_q, &sm.q_full, 64, qh, qt);
               }
             }
           }
@@ -970,27 +1012,28 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             bulk_load(sm.raw[s], p.k_raw + tile * 8192, 8192, &sm.raw_full[s]);
             bulk_load(sm.raw[s] + 8192, p.k_scale_bytes + tile * 1024, 1024, &sm.raw_full[s]);
           } else {
-            const int s = k_seq % NK;
+            const int s = k_seq % nk_ring;
+            uint8_t* kdst = k_stage_ptr(s);
             MSA_TBEGIN
-            ok = mbar_wait(&sm.k_empty[s], ((k_seq / NK) & 1) ^ 1, abort_flag);
+            ok = mbar_wait(&sm.k_empty[s], ((k_seq / nk_ring) & 1) ^ 1, abort_flag);
             MSA_TEND(13)
             if (!ok) return;
             ++k_seq;
             mbar_expect_tx(&sm.k_full[s], Cfg::kKBytes);
             if constexpr (Cfg::kKDirectFp8) {
               if (p.paged)
-                tma_load_4d(sm.k[s], &tmap_k, &sm.k_full[s], 0, 0, info.g, phys);
+                tma_load_4d(kdst, &tmap_k, &sm.k_full[s], 0, 0, info.g, phys);
               else
-                tma_load_3d(sm.k[s], &tmap_k, &sm.k_full[s], 0, info.g, tok_k);
+                tma_load_3d(kdst, &tmap_k, &sm.k_full[s], 0, info.g, tok_k);
             } else if (p.paged) {
-              tma_load_4d(sm.k[s], &tmap_k, &sm.k_full[s], 0, 0, info.g, phys);
-              tma_load_4d(sm.k[s] + kHalfBytes, &tmap_k, &sm.k_full[s], 64, 0, info.g, phys);
+              tma_load_4d(kdst, &tmap_k, &sm.k_full[s], 0, 0, info.g, phys);
+              tma_load_4d(kdst + kHalfBytes, &tmap_k, &sm.k_full[s], 64, 0, info.g, phys);
             } else {
-              tma_load_3d(sm.k[s], &tmap_k, &sm.k_full[s], 0, info.g, tok_k);
-              tma_load_3d(sm.k[s] + kHalfBytes, &tmap_k, &sm.k_full[s], 64, info.g, tok_k);
+              tma_load_3d(kdst, &tmap_k, &sm.k_full[s], 0, info.g, tok_k);
+              tma_load_3d(kdst + kHalfBytes, &tmap_k, &sm.k_full[s], 64, info.g, tok_k);
             }
           }
-          if (!p.do_pv) return;
+          if (!kDoPv) return;
           // ---- V ----
           if constexpr (Cfg::kVConvert) {
             const int s = raw_seq % NRAW;
@@ -1057,11 +1100,12 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // =======================================================================
       bool ok = true;
       uint32_t n_q = 0, k_seq = 0, v_seq = 0, it_total = 0;
-      int j = 0;
-      for (int item = item0; item < p.n_items && ok; item += item_step, ++j) {
+      for (int j = 0; ok; ++j) {
+        const int item = item_of(j);
+        if (item < 0) break;
         const int b = j & 1;
         int count;
-        if (p.sparse) {
+        if (sparse) {
           ok = mbar_wait(&sm.bm_full[b], (j >> 1) & 1, abort_flag);
           if (!ok) break;
           count = sm.item_pages[b];
@@ -1074,13 +1118,13 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           MSA_TEND(14)
           if (lane == 0) { MSA_TRACE(14, it_total, clock64()) }
           ++n_q;
-          if (!p.do_pv) {
+          if (!kDoPv) {
             // Score-only pass: nothing but Q K^T, one page after the other into alternating S buffers; the
             // buffer of page n is free once the softmax warps have read page n - 2 out of it.
             for (int i = 0; i < count && ok; ++i, ++it_total) {
-              const int ks = k_seq % NK;
+              const int ks = k_seq % nk_ring;
               MSA_TBEGIN
-              ok = mbar_wait(&sm.k_full[ks], (k_seq / NK) & 1, abort_flag);
+              ok = mbar_wait(&sm.k_full[ks], (k_seq / nk_ring) & 1, abort_flag);
               MSA_TEND(6)
               ++k_seq;
               const int sb = it_total & 1;
@@ -1090,17 +1134,18 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
               if (!ok) break;
               tc_fence_after();
               if (lane == 0) {
-                issue_qk_stage<Cfg, Smem, 0>(sm, ks, sb * 256, p.half_dim != 0);
+                const uint32_t kaddr = smem_u32(k_stage_ptr(ks));
+                issue_qk_at<Cfg, Smem, 0>(sm, kaddr, sb * 256, p.half_dim != 0);
                 umma_commit(&sm.sc_full[0][sb]);
                 if constexpr (NT == 2) {
-                  issue_qk_stage<Cfg, Smem, NT - 1>(sm, ks, sb * 256, p.half_dim != 0);
+                  issue_qk_at<Cfg, Smem, NT - 1>(sm, kaddr, sb * 256, p.half_dim != 0);
                   umma_commit(&sm.sc_full[NT - 1][sb]);
                 }
                 if (i + 1 == count) umma_commit(&sm.q_empty);   // Q is free after the item's last QK
               }
               __syncwarp();
             }
-            if (p.sparse && lane == 0) mbar_arrive(&sm.bm_empty[b]);
+            if (sparse && lane == 0) mbar_arrive(&sm.bm_empty[b]);
             __syncwarp();
             continue;
           }
@@ -1111,7 +1156,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             const bool has_next = i + 1 < count;
             int v_stage = 0, k_stage = 0;
             uint32_t k_this = 0;
-            if (real && p.do_pv) {
+            if (real && kDoPv) {
               v_stage = v_seq % NV;
               MSA_TBEGIN
               ok = mbar_wait(&sm.v_full[v_stage], (v_seq / NV) & 1, abort_flag);
@@ -1141,7 +1186,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
               tc_fence_after();
               if (lane == 0) {
                 MSA_TRACE(4 + t * 2, it_total, clock64())
-                if (real && p.do_pv) {
+                if (real && kDoPv) {
                   if (t == 0) issue_pv_stage<Cfg, Smem, 0>(sm, v_stage, i > 0 ? 1u : 0u);
                   else issue_pv_stage<Cfg, Smem, NT - 1>(sm, v_stage, i > 0 ? 1u : 0u);
                 }
@@ -1151,7 +1196,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                   umma_commit(&sm.s_full[t]);
                   // the QK just issued for the last tile is the item's last: Q may be overwritten after it
                   if (t == NT - 1 && i + 2 == count) umma_commit(&sm.q_empty);
-                } else if (real && p.do_pv) {
+                } else if (real && kDoPv) {
                   umma_commit(&sm.o_final[t]);
                 }
                 MSA_TRACE(5 + t * 2, it_total, clock64())
@@ -1161,7 +1206,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             if (real) ++it_total;
           }
         }
-        if (p.sparse && lane == 0) mbar_arrive(&sm.bm_empty[b]);
+        if (sparse && lane == 0) mbar_arrive(&sm.bm_empty[b]);
         __syncwarp();
       }
       MSA_TFLUSH(lane == 0, 3, 7)
@@ -1221,15 +1266,16 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
           }
         };
-        int j = 0;
-        for (int item = item0; item < p.n_items && ok; item += item_step, ++j) {
+        for (int j = 0; ok; ++j) {
+          const int item = item_of(j);
+          if (item < 0) break;
           const ItemInfo info = load_item(p, item, NT);
           const int b = j & 1;
-          if (p.sparse) {
+          if (sparse) {
             ok = mbar_wait(&sm.bm_full[b], (j >> 1) & 1, abort_flag);
             if (!ok) break;
           }
-          const int count = p.sparse ? sm.item_pages[b] : info.walk_n;
+          const int count = sparse ? sm.item_pages[b] : info.walk_n;
           for (int pg = 0; pg < count && ok; ++pg) {
             if constexpr (Cfg::kKConvert) {
               const int rs = raw_seq % NRAW, st = k_seq % NK;
@@ -1240,10 +1286,13 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
               ++k_seq;
               convert(sm.raw[rs], sm.k[st] + dst_off);
               fence_proxy_async();
-              mbar_arrive(&sm.k_full[st]);
-              mbar_arrive(&sm.raw_empty[rs]);
+              __syncwarp();
+              if (lane == 0) {
+                mbar_arrive(&sm.k_full[st]);
+                mbar_arrive(&sm.raw_empty[rs]);
+              }
             }
-            if (p.do_pv) {
+            if (kDoPv) {
               const int rs = raw_seq % NRAW, st = v_seq % NV;
               MSA_TBEGIN
               ok = mbar_wait(&sm.raw_full[rs], (raw_seq / NRAW) & 1, abort_flag);
@@ -1257,12 +1306,15 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
               MSA_TBEGIN
               convert(sm.raw[rs], sm.v[st] + dst_off);
               fence_proxy_async();
-              mbar_arrive(&sm.v_full[st]);
-              mbar_arrive(&sm.raw_empty[rs]);
+              __syncwarp();
+              if (lane == 0) {
+                mbar_arrive(&sm.v_full[st]);
+                mbar_arrive(&sm.raw_empty[rs]);
+              }
               MSA_TEND(9)
             }
           }
-          if (p.sparse) {
+          if (sparse) {
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.bm_empty[b]);
           }

@@ -17,8 +17,11 @@ constexpr int kPage = 128;
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+inline int tile_rows_of(const msa_plan_desc* d) { return d->tile_rows == 256 ? 256 : kPage; }
+
 int plan_check(const msa_plan_desc* d) {
   if (d == nullptr || d->batch < 0) return MSA_ERR_INVALID;
+  if (d->tile_rows != 0 && d->tile_rows != 128 && d->tile_rows != 256) return MSA_ERR_INVALID;
   if (d->batch > 0 && (d->qo_lens == nullptr || d->kv_lens == nullptr)) return MSA_ERR_INVALID;
   if (d->num_qo_heads <= 0 || d->num_kv_heads <= 0 || d->num_qo_heads % d->num_kv_heads != 0) return MSA_ERR_INVALID;
   for (int b = 0; b < d->batch; ++b)
@@ -39,7 +42,7 @@ int plan_sizes(const msa_plan_desc* d, int32_t* n_work, int64_t* total_q, int64_
   if (rc != MSA_OK) return rc;
   int64_t nw = 0, tq = 0, tp = 0;
   for (int b = 0; b < d->batch; ++b) {
-    nw += ceil_div(d->qo_lens[b], kPage);
+    nw += ceil_div(d->qo_lens[b], tile_rows_of(d));
     tq += d->qo_lens[b];
     tp += ceil_div(d->kv_lens[b], kPage);
   }
@@ -75,8 +78,9 @@ int plan(const msa_plan_desc* d, int32_t* work, int32_t* kv_page_indptr, int32_t
     int start = 0, kv_base = 0;
     for (int b = 0; b < d->batch; ++b) {
       const int ql = d->qo_lens[b], kl = d->kv_lens[b], off = offset_of(d, b, max_kv);
-      for (int t0 = 0; t0 < ql; t0 += kPage) {
-        const int rows = std::min(kPage, ql - t0);
+      const int tile = tile_rows_of(d);
+      for (int t0 = 0; t0 < ql; t0 += tile) {
+        const int rows = std::min(tile, ql - t0);
         const int64_t vis = d->causal ? std::min<int64_t>(kl, static_cast<int64_t>(t0) + rows + off) : kl;
         Tile t;
         t.cost = static_cast<int>(std::max<int64_t>(0, ceil_div(vis, kPage)));
