@@ -335,6 +335,231 @@ topk_select_kernel(const float* __restrict__ ms, int H, int K, int T, int nvp, i
   }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Fast path: at most 1024 candidate pages per row, token count a multiple of 4 (the prefill and decode shapes).
+// A CTA owns 16 consecutive tokens of one head: the [K x 16] slab goes to shared memory once (cp.async, 64-byte
+// global segments), and the selection never sorts more than a few dozen values per row:
+//   A. every row is cut into G = 2 * TOPK interleaved groups (group = page mod G, so that a run of visible pages
+//      spreads over all groups); 16 threads per row take their groups' maxima.  The TOPK-th largest group maximum
+//      is a lower bound `thr` of the TOPK-th largest score, and only ~1.5 * TOPK scores reach it.
+//   B. the same threads collect the scores >= thr (and > -inf) as (score, page) candidates, at most 4 * TOPK;
+//   C. a warp ranks a row's candidates against each other (score descending, page ascending: the lower page wins
+//      a tie), keeps rank < TOPK, and writes the kept pages in ascending order.
+// A row with more candidates than the buffer holds (masses of equal scores) is redone by its warp with a
+// bit-by-bit search of the TOPK-th largest key over the slab: slower, exact, and rare.
+// Semantics are those of topk_select_kernel: forced tiles rank as FLT_MAX, NaN never wins, +inf ranks with
+// FLT_MAX, -0.0 ties with +0.0, a pick scoring -inf is not reported (-1 at the tail).
+// ---------------------------------------------------------------------------------------------------
+constexpr int kFastTok = 16;
+
+template <int TOPK>
+struct TopkFastSmem {
+  static constexpr int G = 2 * TOPK;      // groups per row
+  static constexpr int C = 4 * TOPK;      // candidate capacity per row
+  float slab[kTopkChunk][kFastTok];
+  float gmax[G][kFastTok];
+  float cand_v[kFastTok][C];
+  short cand_k[kFastTok][C];
+  short sel[kFastTok][TOPK];
+  float thr[kFastTok];
+  int cnt[kFastTok];
+};
+
+template <int TOPK>
+__global__ void __launch_bounds__(256, 2)
+topk_select_fast_kernel(const float* __restrict__ ms, int H, int K, int T, int nvp, int force_begin, int force_end,
+                        int* __restrict__ out) {
+  using Smem = TopkFastSmem<TOPK>;
+  constexpr int G = Smem::G, C = Smem::C;
+  constexpr int GPT = G / 16;              // groups per thread (16 threads per row)
+  extern __shared__ __align__(16) uint8_t topk_raw[];
+  Smem& sm = *reinterpret_cast<Smem*>(topk_raw);
+
+  const int h = blockIdx.y;
+  const int t0 = blockIdx.x * kFastTok;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int keff = min(K, nvp);            // <= 1024 (host)
+  const float* base = ms + static_cast<size_t>(h) * K * T + t0;
+  const int ntok = min(kFastTok, T - t0);  // a multiple of 4 (host: T % 4 == 0)
+
+  // ---- slab in: 16-byte pieces, all in flight at once ---------------------------------------------------
+  for (int idx = tid; idx < keff * 4; idx += 256) {
+    const int k = idx >> 2, q4 = idx & 3;
+    float* dst = &sm.slab[k][q4 * 4];
+    if (q4 * 4 < ntok) {
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)),
+                   "l"(base + static_cast<size_t>(k) * T + q4 * 4)
+                   : "memory");
+    } else {
+      *reinterpret_cast<float4*>(dst) = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    }
+  }
+  if (tid < kFastTok) sm.cnt[tid] = 0;
+  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+  __syncthreads();
+  // forced tiles rank above everything (at most TOPK rows of the slab)
+  for (int idx = tid; idx < (force_begin + force_end) * kFastTok; idx += 256) {
+    const int f = idx / kFastTok, tt = idx % kFastTok;
+    const int k = f < force_begin ? f : nvp - force_end + (f - force_begin);
+    if (k >= 0 && k < keff) sm.slab[k][tt] = 3.402823466e38f;
+  }
+  if (force_begin + force_end > 0) __syncthreads();
+
+  // ---- A: group maxima.  Thread (u, t): pages u, u + 16, u + 32, ...; page u + 16 i belongs to group
+  // (u + 16 i) mod G, i.e. local group i mod GPT ------------------------------------------------------------
+  const int t = lane & 15, u = warp * 2 + (lane >> 4);
+  float gm[GPT];
+#pragma unroll
+  for (int j = 0; j < GPT; ++j) gm[j] = -INFINITY;
+  bool saw_inf = false;
+  for (int i0 = 0; i0 < 64; i0 += GPT) {
+#pragma unroll
+    for (int j = 0; j < GPT; ++j) {
+      const int k = u + 16 * (i0 + j);
+      if (k < keff) {
+        const float v = sm.slab[k][t];
+        saw_inf |= (v == INFINITY);
+        gm[j] = fmaxf(gm[j], v);           // NaN never wins
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < GPT; ++j) sm.gmax[u + 16 * j][t] = fminf(gm[j], 3.402823466e38f);
+  // +inf ranks with FLT_MAX: rewrite such scores in place (rare, CTA-uniform branch)
+  if (__syncthreads_or(saw_inf ? 1 : 0)) {
+    for (int i = 0; i < 64; ++i) {
+      const int k = u + 16 * i;
+      if (k < keff && sm.slab[k][t] == INFINITY) sm.slab[k][t] = 3.402823466e38f;
+    }
+    __syncthreads();
+  }
+
+  // ---- threshold of each row: the TOPK-th largest of its G group maxima (warp w: rows 2w, 2w + 1) ------------
+  for (int rr = 0; rr < 2; ++rr) {
+    const int row = warp * 2 + rr;
+    float mine[G / 32];
+#pragma unroll
+    for (int a = 0; a < G / 32; ++a) mine[a] = sm.gmax[lane + 32 * a][row];
+    int rank[G / 32];
+#pragma unroll
+    for (int a = 0; a < G / 32; ++a) rank[a] = 0;
+    for (int b = 0; b < G; ++b) {
+      const float vb = sm.gmax[b][row];    // broadcast read
+#pragma unroll
+      for (int a = 0; a < G / 32; ++a) {
+        const int ia = lane + 32 * a;
+        rank[a] += (vb > mine[a] || (vb == mine[a] && b < ia)) ? 1 : 0;
+      }
+    }
+#pragma unroll
+    for (int a = 0; a < G / 32; ++a)
+      if (rank[a] == TOPK - 1) sm.thr[row] = mine[a];
+  }
+  __syncthreads();
+
+  // ---- B: candidates ------------------------------------------------------------------------------------------
+  {
+    const float thr = sm.thr[t];
+    for (int i = 0; i < 64; ++i) {
+      const int k = u + 16 * i;
+      if (k < keff) {
+        const float v = sm.slab[k][t];
+        if (v >= thr && v > -INFINITY) {
+          const int slot = atomicAdd(&sm.cnt[t], 1);
+          if (slot < C) {
+            sm.cand_v[t][slot] = v + 0.0f;   // -0.0 -> +0.0
+            sm.cand_k[t][slot] = static_cast<short>(k);
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- C: rank, keep, order, emit (warp w: rows 2w, 2w + 1) --------------------------------------------------
+  for (int rr = 0; rr < 2; ++rr) {
+    const int row = warp * 2 + rr;
+    const int tok = t0 + row;
+    if (tok >= T) continue;                // warp-uniform
+    int* o = out + (static_cast<size_t>(tok) * H + h) * TOPK;
+    const int n = sm.cnt[row];
+    int n_sel = 0;
+    if (n <= C) {
+      // every lane owns candidates lane, lane + 32, ...; rank = number of candidates that beat it
+      for (int a0 = 0; a0 < n; a0 += 32) {
+        const int a = a0 + lane;
+        const float va = a < n ? sm.cand_v[row][a] : 0.f;
+        const int ka = a < n ? sm.cand_k[row][a] : 0;
+        int rank = 0;
+        for (int b = 0; b < n; ++b) {
+          const float vb = sm.cand_v[row][b];
+          const int kb = sm.cand_k[row][b];
+          rank += (vb > va || (vb == va && kb < ka)) ? 1 : 0;
+        }
+        const bool keep = a < n && rank < TOPK;
+        const uint32_t m = __ballot_sync(0xffffffffu, keep);
+        if (keep) sm.sel[row][n_sel + __popc(m & ((1u << lane) - 1u))] = static_cast<short>(ka);
+        n_sel += __popc(m);
+      }
+    } else {
+      // too many candidates (masses of equal scores): search the TOPK-th largest key of the row bit by bit
+      const uint32_t* none = nullptr;
+      (void)none;
+      uint32_t prefix = 0u;
+      int need = TOPK;                     // how many of the keys >= prefix-so-far are still wanted
+      // keys of finite, non-NaN scores; -inf and NaN rank lowest and are never reported
+      auto key_at = [&](int k) -> uint32_t {
+        const float v = sm.slab[k][row];
+        if (!(v == v) || v == -INFINITY) return 0u;
+        return ordered_key(v + 0.0f);
+      };
+      for (int bit = 31; bit >= 0; --bit) {
+        const uint32_t trial = prefix | (1u << bit);
+        int c = 0;
+        for (int k = lane; k < keff; k += 32) {
+          const uint32_t key = key_at(k);
+          c += ((key >> bit) == (trial >> bit)) ? 1 : 0;   // keys that match the prefix and have this bit set
+        }
+        c = __reduce_add_sync(0xffffffffu, c);
+        if (c >= need) prefix = trial;       // the TOPK-th largest has this bit set
+        else need -= c;                      // all of those are above it
+      }
+      // prefix = key of the TOPK-th largest (0 if fewer than TOPK reportable scores); `need` of its ties are taken
+      int taken_eq = 0;
+      for (int k0 = 0; k0 < keff; k0 += 32) {
+        const int k = k0 + lane;
+        const uint32_t key = k < keff ? key_at(k) : 0u;
+        const bool gt = key > prefix && key != 0u;
+        const bool eq = key == prefix && key != 0u;
+        const uint32_t me = __ballot_sync(0xffffffffu, eq);
+        const bool eq_take = eq && (taken_eq + __popc(me & ((1u << lane) - 1u)) < need);
+        const bool keep = gt || eq_take;
+        const uint32_t mk = __ballot_sync(0xffffffffu, keep);
+        const int pos = n_sel + __popc(mk & ((1u << lane) - 1u));
+        if (keep && pos < TOPK) sm.sel[row][pos] = static_cast<short>(k);
+        n_sel = min(TOPK, n_sel + __popc(mk));
+        taken_eq += __popc(me);
+      }
+    }
+    __syncwarp();
+    // ascending page order: position = number of kept pages below mine
+    for (int a0 = 0; a0 < TOPK; a0 += 32) {
+      const int a = a0 + lane;
+      if (a < TOPK) {
+        if (a < n_sel) {
+          const int ka = sm.sel[row][a];
+          int pos = 0;
+          for (int b = 0; b < n_sel; ++b) pos += (sm.sel[row][b] < ka) ? 1 : 0;
+          o[pos] = ka;
+        } else {
+          o[a] = -1;                       // slots n_sel .. TOPK-1
+        }
+      }
+    }
+    __syncwarp();
+  }
+}
+
 // [H, K, T] -> [H, K, n_blocks]: max over the tokens of each query block.  A warp owns four consecutive
 // blocks of one (head, page) row and has all their loads in flight before it reduces (one 128-token block is
 // a single 16-byte load per lane, far too little to cover the memory latency on its own).
@@ -400,7 +625,24 @@ static int launch_topk_shape(const float* ms, int H, int K, int T, int nvp, int 
 }
 
 template <int TOPK>
+static int launch_topk_fast(const float* ms, int H, int K, int T, int nvp, int fb, int fe, int* out, cudaStream_t st) {
+  static DeviceSetup setup;
+  constexpr int smem = static_cast<int>(sizeof(TopkFastSmem<TOPK>));
+  const int rc = setup.ensure(nullptr, [] {
+    return static_cast<int>(
+        cudaFuncSetAttribute(topk_select_fast_kernel<TOPK>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  });
+  if (rc != MSA_OK) return rc;
+  dim3 grid((T + kFastTok - 1) / kFastTok, H);
+  topk_select_fast_kernel<TOPK><<<grid, 256, smem, st>>>(ms, H, K, T, nvp, fb, fe, out);
+  return static_cast<int>(cudaGetLastError());
+}
+
+template <int TOPK>
 static int launch_topk(const float* ms, int H, int K, int T, int nvp, int fb, int fe, int* out, cudaStream_t st) {
+  // up to 1024 candidate pages and 16-byte aligned token rows: the slab-in-shared-memory selection
+  if ((K < nvp ? K : nvp) <= kTopkChunk && T % 4 == 0 && (reinterpret_cast<uintptr_t>(ms) & 15) == 0)
+    return launch_topk_fast<TOPK>(ms, H, K, T, nvp, fb, fe, out, st);
   // fewer wide CTAs than two per SM (decode-sized inputs): the narrow shape gives every row its own warp
   // and four times as many CTAs
   static DeviceSetup setup;
