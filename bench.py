@@ -471,7 +471,7 @@ def run_c5_sharded(dev, rank, world, dist, n_req=8, length=32768, hq_total=64, h
     hr = hq_total // hkv_total
     lens = (length,) * n_req
     T, n_pages, ppr = sum(lens), sum(lens) // PAGE, length // PAGE
-    my_heads = list(range(rank, hkv_total, world))
+    my_heads = msa_b200.shard_kv_heads(hkv_total, world, rank)
     qo = torch.tensor(lens)
     plan = msa_b200.fmha_sm100_plan(qo, qo, hr, num_kv_heads=1, page_size=PAGE, kv_block_num=topk,
                                     sparse_kernel_mode="prefill", device=dev)
@@ -599,6 +599,8 @@ def cpu_sample_rate(seed, target_s=12.0, max_blocks=64):
 def run_reference_arm(args, rank):
     if rank != 0:
         return
+    # torchrun exports OMP_NUM_THREADS=1 to every rank: the CPU arm takes all host threads explicitly
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
     cores = torch.get_num_threads()
     per_step = max(2.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
     vals = []
@@ -887,6 +889,7 @@ def main():
     if rank == 0:
         line["clocks"] = clocks
         if not args.no_cpu and not args.no_extras:
+            torch.set_num_threads(max(1, os.cpu_count() or 1))
             tf, dt, n = cpu_sample_rate(7)
             line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
                                     "sample": f"last {n} 128-query blocks of the 16384-token request x {HQ} heads x "

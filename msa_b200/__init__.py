@@ -7,7 +7,8 @@ from .sparse import (SparseDecodePagedAttentionWrapper, build_k2q_csr, k2q_csr_t
                      sparse_atten_func, sparse_atten_nvfp4_kv_func, sparse_decode_atten_func, sparse_prefill_nvfp4)
 from .host_pipeline import HostPrefillPipeline  # noqa: F401
 from .kv_cache import absmax_bf16, append_kv_fp8, append_kv_nvfp4  # noqa: F401
-from .shard import request_cost, scatter_rows, shard_batch, shard_requests  # noqa: F401
+from .shard import (gather_heads, head_shard, request_cost, scatter_rows, shard_batch, shard_kv_heads,  # noqa: F401
+                    shard_requests)
 from ._lib import MsaError, build_library, get_lib  # noqa: F401
 
 __version__ = "0.1.0"

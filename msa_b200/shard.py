@@ -93,3 +93,31 @@ def scatter_rows(dst, shard: Dict[str, object], src) -> None:
         at += e - s
     if at != src.shape[0]:
         raise ValueError("shard output has %d rows, its requests hold %d" % (src.shape[0], at))
+
+
+def shard_kv_heads(num_kv_heads: int, world_size: int, rank: int) -> List[int]:
+    """KV heads of rank ``rank`` when a batch is split by KV-head group: heads ``rank, rank + world_size, ...``.
+
+    With ``world_size == num_kv_heads`` every GPU holds exactly one KV head and the query heads that attend to it
+    (how the NVFP4 prefill case of the benchmark is spread over 8 GPUs).  Like the request split this needs no
+    collective on the data path: attention never mixes KV heads.
+    """
+    if world_size < 1 or not 0 <= rank < world_size:
+        raise ValueError("rank out of range")
+    return list(range(rank, int(num_kv_heads), world_size))
+
+
+def head_shard(kv_head: int, num_qo_heads: int, num_kv_heads: int) -> Dict[str, object]:
+    """Index ranges of one KV-head group: ``q_heads`` (slice of the query-head axis of Q and O), ``kv_head``
+    (index into the head axis of paged K/V and, for page lists given per KV head, of ``kv_block_indexes``)."""
+    if num_qo_heads % num_kv_heads:
+        raise ValueError("num_qo_heads must be a multiple of num_kv_heads")
+    hr = num_qo_heads // num_kv_heads
+    if not 0 <= kv_head < num_kv_heads:
+        raise ValueError("kv_head out of range")
+    return dict(kv_head=int(kv_head), q_heads=slice(kv_head * hr, (kv_head + 1) * hr), heads_per_kv=hr)
+
+
+def gather_heads(dst, kv_head: int, num_qo_heads: int, num_kv_heads: int, src) -> None:
+    """Copy one head group's output ``src[total_q, hr, D]`` into its query-head columns of ``dst[total_q, Hq, D]``."""
+    dst[:, head_shard(kv_head, num_qo_heads, num_kv_heads)["q_heads"]] = src

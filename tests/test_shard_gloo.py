@@ -12,7 +12,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from msa_b200.shard import request_cost, scatter_rows, shard_batch, shard_requests
+from msa_b200.shard import (gather_heads, head_shard, request_cost, scatter_rows, shard_batch, shard_kv_heads,
+                            shard_requests)
 from oracle import msa_oracle as O
 from util import make_paged
 
@@ -95,6 +96,47 @@ def test_two_ranks_reproduce_the_single_process_result():
     assert sorted(r for p in reqs for r in p) == list(range(len(QO)))
     assert all(len(p) > 0 for p in reqs)
     assert t_max == 11.0
+    q, k, v, table, idx = _problem()
+    ref, _ = O.sparse_attention_paged(q, k, v, table, QO, KV, idx)
+    assert torch.equal(out, ref.float())
+
+
+def _head_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        q, k, v, table, idx = _problem()
+        outs = []
+        for g in shard_kv_heads(HKV, world, rank):
+            hs = head_shard(g, HQ, HKV)
+            # this rank's slice of the problem: its KV head, the query heads on it, its page lists
+            o, _ = O.sparse_attention_paged(q[:, hs["q_heads"]], k[:, g:g + 1], v[:, g:g + 1], table, QO, KV,
+                                            idx[:, g:g + 1])
+            outs.append((g, o))
+        gathered = [None] * world
+        dist.all_gather_object(gathered, outs)              # what the benchmark does with NCCL all_gather
+        if rank == 0:
+            full = torch.zeros(sum(QO), HQ, 128)
+            for part in gathered:
+                for g, o in part:
+                    gather_heads(full, g, HQ, HKV, o)
+            ret["out"] = full
+            ret["heads"] = [[g for g, _ in part] for part in gathered]
+    finally:
+        dist.destroy_process_group()
+
+
+def test_kv_head_split_two_ranks_reproduce_the_single_process_result():
+    """Split by KV-head group (the 8-GPU NVFP4 case, here 2 KV heads on 2 gloo ranks): each rank attends with its
+    KV head only, the gathered outputs equal the unsplit result bit for bit."""
+    assert shard_kv_heads(8, 8, 3) == [3] and shard_kv_heads(8, 2, 1) == [1, 3, 5, 7] and shard_kv_heads(8, 16, 9) == []
+    assert head_shard(3, 64, 8)["q_heads"] == slice(24, 32)
+    world = 2
+    with mp.Manager() as m:
+        ret = m.dict()
+        mp.spawn(_head_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+        out, heads = ret["out"], ret["heads"]
+    assert heads == [[0], [1]]
     q, k, v, table, idx = _problem()
     ref, _ = O.sparse_attention_paged(q, k, v, table, QO, KV, idx)
     assert torch.equal(out, ref.float())
