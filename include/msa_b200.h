@@ -305,6 +305,15 @@ int msa_absmax_bf16(const void* x, int64_t n, float* out, void* stream);
 int msa_umma_selftest(const void* q, const void* k, const void* v, const void* p, float* s_out, float* o_out,
                       int32_t* status, void* stream);
 
+/* The same kernel with its operand loads withheld, so that its first bounded wait runs out after `wait_cycles`
+ * GPU clock cycles (<= 0 or above the library's limit: the library's limit): every later step is skipped, TMEM
+ * is released, the kernel returns normally and *status reads MSA_ERR_TIMEOUT.  This is how the timeout path
+ * every kernel of the library shares (bounded mbarrier wait -> CTA-wide abort flag -> teardown -> status word)
+ * is exercised without faulting or hanging anything; the outputs are left untouched.  No counterpart in the
+ * reference, whose waits are unbounded. */
+int msa_umma_selftest_timeout(const void* q, const void* k, const void* v, const void* p, float* s_out,
+                              float* o_out, int32_t* status, int64_t wait_cycles, void* stream);
+
 /* Role cycle accounting for the attention kernel: int64 [n_ctas, 16] device buffer, or NULL to stop.
  * Only libraries built with -DMSA_ROLE_TIMING write to it (the default build ignores it).  Stands in for the
  * reference's GPU_TRACE / SM_TIMING builds (python/fmha_sm100/csrc/include/gpu_trace.h). */

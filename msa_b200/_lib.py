@@ -167,6 +167,8 @@ def _bind(lib):
     lib.msa_debug_set_timing_buffer.argtypes = [vp]
     lib.msa_umma_selftest.restype = c_int32
     lib.msa_umma_selftest.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp]
+    lib.msa_umma_selftest_timeout.restype = c_int32
+    lib.msa_umma_selftest_timeout.argtypes = [vp, vp, vp, vp, vp, vp, vp, c_int64, vp]
     return lib
 
 

@@ -92,7 +92,12 @@ void msa_debug_set_timing_buffer(void* buffer) { msa::set_timing_buffer(buffer);
 
 int msa_umma_selftest(const void* q, const void* k, const void* v, const void* p, float* s_out, float* o_out,
                       int32_t* status, void* stream) {
-  return msa::umma_selftest(q, k, v, p, s_out, o_out, status, static_cast<cudaStream_t>(stream));
+  return msa::umma_selftest(q, k, v, p, s_out, o_out, status, 0, 0, static_cast<cudaStream_t>(stream));
+}
+
+int msa_umma_selftest_timeout(const void* q, const void* k, const void* v, const void* p, float* s_out,
+                              float* o_out, int32_t* status, int64_t wait_cycles, void* stream) {
+  return msa::umma_selftest(q, k, v, p, s_out, o_out, status, 1, wait_cycles, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -50,16 +50,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // CTA-wide abort flag, and every other waiter that sees the flag gives up too,
 // so the CTA always reaches its teardown (TMEM free) and the host reads
 // MSA_ERR_TIMEOUT from the status word instead of a hung GPU.
-constexpr long long kWaitCycles = 1LL << 29;  // ~0.3 s at 2 GHz
+#ifndef MSA_WAIT_CYCLES
+#define MSA_WAIT_CYCLES (1LL << 29)  // ~0.3 s at 2 GHz; a build may shorten it with -DMSA_WAIT_CYCLES=...
+#endif
+constexpr long long kWaitCycles = MSA_WAIT_CYCLES;
 
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          long long limit = kWaitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if (((++spins) & 0xff) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitCycles) {
+      if (clock64() - t0 > limit) {
         *abort_flag = 1;
         return false;
       }

@@ -270,7 +270,8 @@ struct __align__(1024) SelfTestSmem {
 __global__ void __launch_bounds__(128, 1)
 umma_selftest_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                      const __grid_constant__ CUtensorMap tmap_v, const __nv_bfloat16* __restrict__ pmat,
-                     float* __restrict__ s_out, float* __restrict__ o_out, int* status) {
+                     float* __restrict__ s_out, float* __restrict__ o_out, int* status, int skip_loads,
+                     long long wait_limit) {
   extern __shared__ uint8_t smem_raw[];
   SelfTestSmem& sm = *reinterpret_cast<SelfTestSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -290,7 +291,9 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
-  if (tid == 0) {
+  // skip_loads: the loads are never issued, so the wait below can only run out -- the way a test drives the
+  // timeout path (abort flag, every later step skipped, TMEM freed, status word written) without a fault
+  if (tid == 0 && !skip_loads) {
     mbar_expect_tx(&sm.full, 3 * kTileBytes);
     tma_load_3d(sm.q, &tmap_q, &sm.full, 0, 0, 0);
     tma_load_3d(sm.q + kHalfBytes, &tmap_q, &sm.full, 64, 0, 0);
@@ -299,7 +302,7 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     tma_load_3d(sm.v, &tmap_v, &sm.full, 0, 0, 0);
     tma_load_3d(sm.v + kHalfBytes, &tmap_v, &sm.full, 64, 0, 0);
   }
-  bool ok = mbar_wait(&sm.full, 0, abort_flag);
+  bool ok = mbar_wait(&sm.full, 0, abort_flag, wait_limit);
   constexpr uint32_t idesc_qk = make_idesc(128, 128, 1, 1, 0, 0);
   constexpr uint32_t idesc_pv = make_idesc(128, 128, 1, 1, 0, 1);
   if (ok && tid == 0) {
@@ -312,7 +315,7 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     umma_commit(&sm.done_s);
   }
   __syncwarp();
-  if (ok) ok = mbar_wait(&sm.done_s, 0, abort_flag);
+  if (ok) ok = mbar_wait(&sm.done_s, 0, abort_flag, wait_limit);
   const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
   const int row = tid;
   if (ok) {
@@ -342,7 +345,7 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     umma_commit(&sm.done_o);
   }
   __syncwarp();
-  if (ok) ok = mbar_wait(&sm.done_o, 0, abort_flag);
+  if (ok) ok = mbar_wait(&sm.done_o, 0, abort_flag, wait_limit);
   if (ok) {
     tc_fence_after();
     uint32_t rg[32];
@@ -362,7 +365,7 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 }
 
 int umma_selftest(const void* q, const void* k, const void* v, const void* pm, float* s_out, float* o_out,
-                  int* status, cudaStream_t st) {
+                  int* status, int skip_loads, long long wait_cycles, cudaStream_t st) {
   if (!q || !k || !v || !pm || !s_out || !o_out || !status) return MSA_ERR_INVALID;
   CUtensorMap mq, mk, mv;
   int rc = make_q_map(&mq, q, 128, 1);
@@ -376,8 +379,9 @@ int umma_selftest(const void* q, const void* k, const void* v, const void* pm, f
         cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   });
   if (rc != MSA_OK) return rc;
+  if (wait_cycles <= 0 || wait_cycles > kWaitCycles) wait_cycles = kWaitCycles;
   umma_selftest_kernel<<<1, 128, smem, st>>>(mq, mk, mv, static_cast<const __nv_bfloat16*>(pm), s_out, o_out,
-                                              status);
+                                              status, skip_loads, wait_cycles);
   return static_cast<int>(cudaGetLastError());
 }
 

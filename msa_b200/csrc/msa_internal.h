@@ -52,7 +52,7 @@ int list_uniformity(const int32_t* work, int n_work, const int32_t* lists, int l
 // 4-D TMA map over paged e4m3 K or V [pages, Hkv, 128, 128]: one 128x128-byte box per (page, head), 128-byte swizzle
 int make_paged_e4m3_map(void* tensor_map, const void* kv, int64_t pages, int hkv);
 int umma_selftest(const void* q, const void* k, const void* v, const void* p, float* s_out, float* o_out,
-                  int* status, cudaStream_t st);
+                  int* status, int skip_loads, long long wait_cycles, cudaStream_t st);
 int decode_fwd(const msa_decode_args* a, cudaStream_t st);
 size_t decode_workspace_bytes(int n_tokens, int num_qo_heads, int num_splits);
 int decode_fwd_static(const msa_decode_args* a, cudaStream_t st);

@@ -366,7 +366,7 @@ struct TopkFastSmem {
 };
 
 template <int TOPK>
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(256, TOPK == 16 ? 3 : 2)
 topk_select_fast_kernel(const float* __restrict__ ms, int H, int K, int T, int nvp, int force_begin, int force_end,
                         int* __restrict__ out) {
   using Smem = TopkFastSmem<TOPK>;
@@ -382,20 +382,30 @@ topk_select_fast_kernel(const float* __restrict__ ms, int H, int K, int T, int n
   const float* base = ms + static_cast<size_t>(h) * K * T + t0;
   const int ntok = min(kFastTok, T - t0);  // a multiple of 4 (host: T % 4 == 0)
 
-  // ---- slab in: 16-byte pieces, all in flight at once ---------------------------------------------------
-  for (int idx = tid; idx < keff * 4; idx += 256) {
-    const int k = idx >> 2, q4 = idx & 3;
-    float* dst = &sm.slab[k][q4 * 4];
-    if (q4 * 4 < ntok) {
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)),
-                   "l"(base + static_cast<size_t>(k) * T + q4 * 4)
-                   : "memory");
-    } else {
-      *reinterpret_cast<float4*>(dst) = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+  // ---- slab in: 16-byte pieces, all in flight at once, in two groups (pages below / from 512) so that the
+  // group maxima of the first half are taken while the second half is still arriving ------------------------------
+  const int ksplit = min(keff, 512);
+  auto load_rows = [&](int k_begin, int k_end) {
+    for (int idx = k_begin * 4 + tid; idx < k_end * 4; idx += 256) {
+      const int k = idx >> 2, q4 = idx & 3;
+      float* dst = &sm.slab[k][q4 * 4];
+      if (q4 * 4 < ntok) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)),
+                     "l"(base + static_cast<size_t>(k) * T + q4 * 4)
+                     : "memory");
+      } else {
+        *reinterpret_cast<float4*>(dst) = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+      }
     }
-  }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  load_rows(0, ksplit);
+  load_rows(ksplit, keff);
   if (tid < kFastTok) sm.cnt[tid] = 0;
-  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+  const bool forced_any = force_begin + force_end > 0;
+  // forced tiles are patched after the whole slab is in: wait for everything first in that (uncommon) case
+  if (forced_any) asm volatile("cp.async.wait_group 0;" ::: "memory");
+  else asm volatile("cp.async.wait_group 1;" ::: "memory");
   __syncthreads();
   // forced tiles rank above everything (at most TOPK rows of the slab)
   for (int idx = tid; idx < (force_begin + force_end) * kFastTok; idx += 256) {
@@ -403,7 +413,7 @@ topk_select_fast_kernel(const float* __restrict__ ms, int H, int K, int T, int n
     const int k = f < force_begin ? f : nvp - force_end + (f - force_begin);
     if (k >= 0 && k < keff) sm.slab[k][tt] = 3.402823466e38f;
   }
-  if (force_begin + force_end > 0) __syncthreads();
+  if (forced_any) __syncthreads();
 
   // ---- A: group maxima.  Thread (u, t): pages u, u + 16, u + 32, ...; page u + 16 i belongs to group
   // (u + 16 i) mod G, i.e. local group i mod GPT ------------------------------------------------------------
@@ -413,6 +423,10 @@ topk_select_fast_kernel(const float* __restrict__ ms, int H, int K, int T, int n
   for (int j = 0; j < GPT; ++j) gm[j] = -INFINITY;
   bool saw_inf = false;
   for (int i0 = 0; i0 < 64; i0 += GPT) {
+    if (i0 == 32 && !forced_any) {         // pages from 512 on: the second load group
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      __syncthreads();
+    }
 #pragma unroll
     for (int j = 0; j < GPT; ++j) {
       const int k = u + 16 * (i0 + j);
@@ -640,8 +654,14 @@ static int launch_topk_fast(const float* ms, int H, int K, int T, int nvp, int f
 
 template <int TOPK>
 static int launch_topk(const float* ms, int H, int K, int T, int nvp, int fb, int fe, int* out, cudaStream_t st) {
-  // up to 1024 candidate pages and 16-byte aligned token rows: the slab-in-shared-memory selection
-  if ((K < nvp ? K : nvp) <= kTopkChunk && T % 4 == 0 && (reinterpret_cast<uintptr_t>(ms) & 15) == 0)
+  static DeviceSetup setup0;
+  int sms0 = 0;
+  const int rc0 = setup0.ensure(&sms0, [] { return static_cast<int>(MSA_OK); });
+  if (rc0 != MSA_OK) return rc0;
+  // up to 1024 candidate pages, 16-byte aligned token rows and enough rows to fill the GPU with 16-token CTAs:
+  // the slab-in-shared-memory selection (decode-sized inputs keep the warp-per-row kernel below)
+  if ((K < nvp ? K : nvp) <= kTopkChunk && T % 4 == 0 && (reinterpret_cast<uintptr_t>(ms) & 15) == 0 &&
+      static_cast<long long>((T + kFastTok - 1) / kFastTok) * H >= 2LL * sms0)
     return launch_topk_fast<TOPK>(ms, H, K, T, nvp, fb, fe, out, st);
   // fewer wide CTAs than two per SM (decode-sized inputs): the narrow shape gives every row its own warp
   // and four times as many CTAs

@@ -32,6 +32,33 @@ def test_umma_selftest():
     assert (o - p.float() @ v.float()).abs().max() < 1e-3
 
 
+def test_bounded_wait_runs_out_and_the_context_stays_usable():
+    """The timeout path shared by every kernel (bounded mbarrier wait -> abort flag -> teardown with TMEM freed ->
+    status word): the self-test kernel is launched with its operand loads withheld and a wait limit of about a
+    millisecond; it must return normally with MSA_ERR_TIMEOUT in the status word, and an ordinary launch right
+    after it (same process, same context) must compute correctly.  Nothing faults or hangs."""
+    lib = msa_b200.get_lib()
+    from msa_b200.api import _ptr, _stream
+    torch.manual_seed(1)
+    q, k, v = (torch.randn(128, 128, device="cuda").to(torch.bfloat16) for _ in range(3))
+    p = torch.rand(128, 128, device="cuda").to(torch.bfloat16)
+    s = torch.full((128, 128), 7.0, device="cuda")
+    o = torch.full((128, 128), 7.0, device="cuda")
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc = lib.msa_umma_selftest_timeout(_ptr(q), _ptr(k), _ptr(v), _ptr(p), _ptr(s), _ptr(o), _ptr(st), 1 << 21,
+                                       _stream())
+    assert rc == 0
+    torch.cuda.synchronize()                                   # returns: the kernel ended by itself
+    assert int(st.item()) == msa_b200._lib.MSA_ERR_TIMEOUT
+    assert bool((s == 7.0).all()) and bool((o == 7.0).all())  # nothing was computed
+    st.zero_()
+    assert lib.msa_umma_selftest(_ptr(q), _ptr(k), _ptr(v), _ptr(p), _ptr(s), _ptr(o), _ptr(st), _stream()) == 0
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert (s - q.float() @ k.float().T).abs().max() < 1e-3
+    assert (o - p.float() @ v.float()).abs().max() < 1e-3
+
+
 def _quantise(kp, vp, kind):
     """-> (device k, device v, oracle k, oracle v, kwargs for fmha_sm100)"""
     if kind == "bf16":

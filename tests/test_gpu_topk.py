@@ -74,6 +74,9 @@ def test_topk_heavy_ties(H, K, T, topk):
     (2, 1024, 20000, 16, 1024, 1, 1, "ties"),        # few distinct values: the cut falls inside long runs of ties
     (1, 2500, 40000, 16, 2500, 0, 0, "causal"),      # more than 1024 pages
     (2, 64, 19999, 32, 40, 0, 0, "ties"),            # few pages, ragged last CTA
+    (1, 1024, 8192, 64, 1000, 1, 0, "random"),       # k = 64 on the slab-resident kernel (128 groups per row)
+    (1, 1000, 6004, 64, 1000, 0, 2, "ties"),         # k = 64, ties, last CTA holds 4 of its 16 tokens
+    (1, 1024, 20004, 16, 1024, 0, 0, "causal"),      # ragged last CTA of the slab-resident kernel
 ])
 def test_topk_many_rows(H, K, T, topk, nvp, fb, fe, mode):
     g = torch.Generator().manual_seed(K + T + topk)
@@ -82,6 +85,10 @@ def test_topk_many_rows(H, K, T, topk, nvp, fb, fe, mode):
         ms = vals[torch.randint(0, len(vals), (H, K, T), generator=g)]
     else:
         ms = torch.randn(H, K, T, generator=g)
+    if mode == "random":
+        ms[:, 5, ::17] = float("inf")                                    # +inf ranks with FLT_MAX
+        ms[:, 9, ::17] = 3.402823466e38
+        ms[:, 11, 3::29] = float("nan")
     if mode == "causal":
         frontier = 1 + (torch.arange(T) * nvp) // T                      # tokens see a growing prefix of pages
         ms.masked_fill_(torch.arange(K)[None, :, None] >= frontier[None, None, :], float("-inf"))

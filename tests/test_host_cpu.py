@@ -254,3 +254,23 @@ int main(void) {
     assert out[4] == "1" and out[5] == "3999"       # heaviest tile first: the decode token over 4000 keys
     assert 1 <= int(out[6]) <= 16 and out[7] == "0" and out[8] == "-104" and out[9] == "5"
     assert "page pool" in out[10]
+
+
+def test_alias_package_exposes_the_reference_names():
+    """`import fmha_sm100` (the reference's package name) serves the same public names from this library."""
+    import fmha_sm100
+    from fmha_sm100 import sparse as fs
+    assert fmha_sm100.fmha_sm100 is msa_b200.fmha_sm100 and fmha_sm100.fmha_sm100_plan is msa_b200.fmha_sm100_plan
+    assert fmha_sm100.sparse_topk_select is msa_b200.sparse_topk_select
+    assert fmha_sm100.sparse_atten_func is msa_b200.sparse_atten_func          # lazy attribute
+    for n in ("sparse_atten_nvfp4_kv_func", "sparse_decode_atten_func", "SparseDecodePagedAttentionWrapper",
+              "build_k2q_csr", "quantize_kv_bf16_to_nvfp4_128x4"):
+        assert hasattr(fs, n)
+    import inspect
+    sig = inspect.signature(msa_b200.SparseDecodePagedAttentionWrapper.plan)
+    for kw in ("page_table", "seqused_k", "seqlen_q", "max_seqlen_k", "q2k_indices", "num_qo_heads", "num_kv_heads",
+               "head_dim", "enable_cuda_graph", "max_grid_size", "fixed_split_size", "disable_split_kv"):
+        assert kw in sig.parameters, kw
+    sig = inspect.signature(msa_b200.SparseDecodePagedAttentionWrapper.run)
+    for kw in ("softmax_scale", "return_softmax_lse", "out", "lse"):
+        assert kw in sig.parameters, kw
