@@ -206,6 +206,36 @@ int msa_k2q_csr_to_lists(const int32_t* row_ptr, const int32_t* q_indices, const
                          int32_t n_rows, int64_t row_ptr_stride, int64_t q_indices_stride, int64_t total_q,
                          int32_t topk, int32_t* counters, int32_t* out, void* stream);
 
+/* q2k page lists -> k2q CSR, on the device: what `build_k2q_csr` (python/fmha_sm100/cute/sparse_index_utils.py:331,
+ * kernels python/fmha_sm100/cute/src/sm100/build_k2q_csr/build_k2q_csr.cu) produces for callers that feed the
+ * CSR-driven entry points.  Rows are packed block-major (block 0 of every request, then block 1, ...); inside a row
+ * the batch-local query ids ascend; the unused tail of q_indices is -1.  The small metadata arrays (device int32)
+ * describe the batch: queries are cut into chunks of at most 256 that do not cross requests.
+ *   q2k                 [num_kv_heads, total_q, topk] request-local block ids, -1 = unused
+ *   chunk_request / chunk_first_query / chunk_len   [n_chunks]
+ *   cu_seqlens_q        [batch + 1];  request_first_chunk [batch + 1];  request_blocks [batch] (CSR rows per request)
+ *   row_of_block        [batch, max_blocks] CSR row of (request, block)
+ *   workspace           msa_build_k2q_csr_workspace_bytes(...) bytes (cleared by the call)
+ *   row_ptr             [num_kv_heads, total_rows + 1];  q_indices [num_kv_heads, q_indices_stride >= total_q * topk] */
+typedef struct msa_csr_build_args {
+  const int32_t* q2k;
+  const int32_t* chunk_request;
+  const int32_t* chunk_first_query;
+  const int32_t* chunk_len;
+  const int32_t* cu_seqlens_q;
+  const int32_t* request_first_chunk;
+  const int32_t* request_blocks;
+  const int32_t* row_of_block;
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t* row_ptr;
+  int32_t* q_indices;
+  int64_t total_q, q_indices_stride;
+  int32_t num_kv_heads, topk, n_chunks, batch, max_blocks, total_rows;
+} msa_csr_build_args;
+size_t msa_build_k2q_csr_workspace_bytes(int32_t num_kv_heads, int32_t n_chunks, int32_t max_blocks, int32_t total_rows);
+int msa_build_k2q_csr(const msa_csr_build_args* args, void* stream);
+
 /* ---------------------------------------------------------------------------
  * Stage 3 (decode): paged FP8 sparse decode, split-KV + combine.
  * Replaces `run_<variant>` in SparseAttnMode::Sparse for q_len <= 32

@@ -85,6 +85,17 @@ class ValidateArgs(Structure):
     ]
 
 
+class CsrBuildArgs(Structure):
+    _fields_ = [
+        ("q2k", c_void_p), ("chunk_request", c_void_p), ("chunk_first_query", c_void_p), ("chunk_len", c_void_p),
+        ("cu_seqlens_q", c_void_p), ("request_first_chunk", c_void_p), ("request_blocks", c_void_p),
+        ("row_of_block", c_void_p), ("workspace", c_void_p), ("workspace_bytes", c_size_t),
+        ("row_ptr", c_void_p), ("q_indices", c_void_p), ("total_q", c_int64), ("q_indices_stride", c_int64),
+        ("num_kv_heads", c_int32), ("topk", c_int32), ("n_chunks", c_int32), ("batch", c_int32),
+        ("max_blocks", c_int32), ("total_rows", c_int32),
+    ]
+
+
 def _sources():
     return [s for s in SOURCES if os.path.exists(os.path.join(CSRC, s))]
 
@@ -142,6 +153,10 @@ def _bind(lib):
     lib.msa_plan.argtypes = [POINTER(PlanDesc), vp, vp, vp, vp, vp]
     lib.msa_validate_inputs.restype = c_int32
     lib.msa_validate_inputs.argtypes = [POINTER(ValidateArgs), vp]
+    lib.msa_build_k2q_csr_workspace_bytes.restype = c_size_t
+    lib.msa_build_k2q_csr_workspace_bytes.argtypes = [c_int32, c_int32, c_int32, c_int32]
+    lib.msa_build_k2q_csr.restype = c_int32
+    lib.msa_build_k2q_csr.argtypes = [POINTER(CsrBuildArgs), vp]
     lib.msa_k2q_csr_to_lists.restype = c_int32
     lib.msa_k2q_csr_to_lists.argtypes = [vp, vp, vp, vp, vp, c_int32, c_int32, c_int64, c_int64, c_int64, c_int32,
                                          vp, vp, vp]

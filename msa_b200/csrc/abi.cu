@@ -46,6 +46,15 @@ int msa_k2q_csr_to_lists(const int32_t* row_ptr, const int32_t* q_indices, const
                                static_cast<cudaStream_t>(stream));
 }
 
+size_t msa_build_k2q_csr_workspace_bytes(int32_t num_kv_heads, int32_t n_chunks, int32_t max_blocks,
+                                         int32_t total_rows) {
+  return msa::build_k2q_csr_workspace_bytes(num_kv_heads, n_chunks, max_blocks, total_rows);
+}
+
+int msa_build_k2q_csr(const msa_csr_build_args* args, void* stream) {
+  return msa::build_k2q_csr(args, static_cast<cudaStream_t>(stream));
+}
+
 int msa_topk_select(const float* max_score, int32_t num_heads, int32_t max_k_tiles, int32_t total_q, int32_t topk,
                     int32_t num_valid_pages, int32_t force_begin, int32_t force_end, int32_t* out, void* stream) {
   return msa::topk_select(max_score, num_heads, max_k_tiles, total_q, topk, num_valid_pages, force_begin, force_end,

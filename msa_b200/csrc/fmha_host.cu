@@ -78,6 +78,14 @@ static int make_kv_map(CUtensorMap* m, const void* kv, int64_t rows, int hkv, in
   return make_map(m, dt, 3, kv, dims, strides, box, sw);
 }
 
+int make_score_map(void* tensor_map, const float* ms, int H, int K, int T, int box_t, int box_k) {
+  const uint64_t dims[3] = {static_cast<uint64_t>(T), static_cast<uint64_t>(K), static_cast<uint64_t>(H)};
+  const uint64_t strides[2] = {static_cast<uint64_t>(T) * 4, static_cast<uint64_t>(K) * T * 4};
+  const uint32_t box[3] = {static_cast<uint32_t>(box_t), static_cast<uint32_t>(box_k), 1};
+  return make_map(static_cast<CUtensorMap*>(tensor_map), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, ms, dims, strides, box,
+                  CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
 int make_paged_e4m3_map(void* tensor_map, const void* kv, int64_t pages, int hkv) {
   return make_kv_map(static_cast<CUtensorMap*>(tensor_map), kv, pages, hkv, 1, 1, 1);
 }

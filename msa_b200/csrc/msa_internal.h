@@ -51,6 +51,8 @@ int list_uniformity(const int32_t* work, int n_work, const int32_t* lists, int l
                     cudaStream_t st);
 // 4-D TMA map over paged e4m3 K or V [pages, Hkv, 128, 128]: one 128x128-byte box per (page, head), 128-byte swizzle
 int make_paged_e4m3_map(void* tensor_map, const void* kv, int64_t pages, int hkv);
+// 3-D TMA map over a float32 score tensor [H, K, T] (T innermost): boxes of box_k pages x box_t tokens
+int make_score_map(void* tensor_map, const float* ms, int H, int K, int T, int box_t, int box_k);
 int umma_selftest(const void* q, const void* k, const void* v, const void* p, float* s_out, float* o_out,
                   int* status, int skip_loads, long long wait_cycles, cudaStream_t st);
 int decode_fwd(const msa_decode_args* a, cudaStream_t st);
@@ -62,6 +64,8 @@ int plan_sizes(const msa_plan_desc* d, int32_t* n_work, int64_t* total_q, int64_
 int plan(const msa_plan_desc* d, int32_t* work, int32_t* kv_page_indptr, int32_t* token_request, int32_t* token_pos,
          int32_t* num_splits);
 int validate_inputs(const msa_validate_args* a, int64_t* where);
+size_t build_k2q_csr_workspace_bytes(int num_kv_heads, int n_chunks, int max_blocks, int total_rows);
+int build_k2q_csr(const msa_csr_build_args* a, cudaStream_t st);
 int k2q_csr_to_lists(const int* row_ptr, const int* q_indices, const int* row_request, const int* row_block,
                      const int* cu_seqlens_q, int num_kv_heads, int n_rows, int64_t row_ptr_stride,
                      int64_t q_indices_stride, int64_t total_q, int topk, int* counters, int* out, cudaStream_t st);

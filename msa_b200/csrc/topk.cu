@@ -353,10 +353,12 @@ topk_select_kernel(const float* __restrict__ ms, int H, int K, int T, int nvp, i
 constexpr int kFastTok = 16;
 
 template <int TOPK>
-struct TopkFastSmem {
+struct __align__(128) TopkFastSmem {
   static constexpr int G = 2 * TOPK;      // groups per row
   static constexpr int C = 4 * TOPK;      // candidate capacity per row
-  float slab[kTopkChunk][kFastTok];
+  float slab[kTopkChunk][kFastTok];       // four TMA boxes of 256 pages x 16 tokens
+  uint64_t full[2];                       // pages [0, 512) / [512, 1024) have landed
+  int abort;
   float gmax[G][kFastTok];
   float cand_v[kFastTok][C];
   short cand_k[kFastTok][C];
@@ -367,46 +369,49 @@ struct TopkFastSmem {
 
 template <int TOPK>
 __global__ void __launch_bounds__(256, TOPK == 16 ? 3 : 2)
-topk_select_fast_kernel(const float* __restrict__ ms, int H, int K, int T, int nvp, int force_begin, int force_end,
-                        int* __restrict__ out) {
+topk_select_fast_kernel(const __grid_constant__ CUtensorMap tmap_ms, int H, int K, int T, int nvp, int force_begin,
+                        int force_end, int* __restrict__ out, int* status) {
   using Smem = TopkFastSmem<TOPK>;
   constexpr int G = Smem::G, C = Smem::C;
   constexpr int GPT = G / 16;              // groups per thread (16 threads per row)
-  extern __shared__ __align__(16) uint8_t topk_raw[];
+  extern __shared__ __align__(128) uint8_t topk_raw[];
   Smem& sm = *reinterpret_cast<Smem*>(topk_raw);
 
   const int h = blockIdx.y;
   const int t0 = blockIdx.x * kFastTok;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int keff = min(K, nvp);            // <= 1024 (host)
-  const float* base = ms + static_cast<size_t>(h) * K * T + t0;
-  const int ntok = min(kFastTok, T - t0);  // a multiple of 4 (host: T % 4 == 0)
+  volatile int* abort_flag = &sm.abort;
 
-  // ---- slab in: 16-byte pieces, all in flight at once, in two groups (pages below / from 512) so that the
-  // group maxima of the first half are taken while the second half is still arriving ------------------------------
-  const int ksplit = min(keff, 512);
-  auto load_rows = [&](int k_begin, int k_end) {
-    for (int idx = k_begin * 4 + tid; idx < k_end * 4; idx += 256) {
-      const int k = idx >> 2, q4 = idx & 3;
-      float* dst = &sm.slab[k][q4 * 4];
-      if (q4 * 4 < ntok) {
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)),
-                     "l"(base + static_cast<size_t>(k) * T + q4 * 4)
-                     : "memory");
+  // ---- slab in: four TMA boxes (256 pages x 16 tokens, 16 KiB each), issued by one thread; the group maxima of
+  // the first two are taken while the last two are still arriving.  Pages past K and tokens past T read zero
+  // (TMA fill) and are never looked at: every loop below stops at keff, and rows past T are not emitted. --------
+  if (tid == 0) {
+    mbar_init(&sm.full[0], 1);
+    mbar_init(&sm.full[1], 1);
+    sm.abort = 0;
+    mbar_fence_init();
+  }
+  if (tid < kFastTok) sm.cnt[tid] = 0;
+  __syncthreads();
+  if (tid == 0) {
+    tma_prefetch_desc(&tmap_ms);
+    for (int half = 0; half < 2; ++half) {
+      const int boxes = max(0, min(2, (keff - half * 512 + 255) / 256));
+      if (boxes > 0) {
+        mbar_expect_tx(&sm.full[half], boxes * 256 * kFastTok * 4);
+        for (int b = 0; b < boxes; ++b)
+          tma_load_3d(&sm.slab[half * 512 + b * 256][0], &tmap_ms, &sm.full[half], t0, half * 512 + b * 256, h);
       } else {
-        *reinterpret_cast<float4*>(dst) = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        mbar_arrive(&sm.full[half]);
       }
     }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-  };
-  load_rows(0, ksplit);
-  load_rows(ksplit, keff);
-  if (tid < kFastTok) sm.cnt[tid] = 0;
+  }
   const bool forced_any = force_begin + force_end > 0;
+  bool ok = mbar_wait(&sm.full[0], 0, abort_flag);
   // forced tiles are patched after the whole slab is in: wait for everything first in that (uncommon) case
-  if (forced_any) asm volatile("cp.async.wait_group 0;" ::: "memory");
-  else asm volatile("cp.async.wait_group 1;" ::: "memory");
-  __syncthreads();
+  if (forced_any && ok) ok = mbar_wait(&sm.full[1], 0, abort_flag);
+  if (forced_any) __syncthreads();
   // forced tiles rank above everything (at most TOPK rows of the slab)
   for (int idx = tid; idx < (force_begin + force_end) * kFastTok; idx += 256) {
     const int f = idx / kFastTok, tt = idx % kFastTok;
@@ -421,22 +426,20 @@ topk_select_fast_kernel(const float* __restrict__ ms, int H, int K, int T, int n
   float gm[GPT];
 #pragma unroll
   for (int j = 0; j < GPT; ++j) gm[j] = -INFINITY;
-  bool saw_inf = false;
-  for (int i0 = 0; i0 < 64; i0 += GPT) {
-    if (i0 == 32 && !forced_any) {         // pages from 512 on: the second load group
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-      __syncthreads();
-    }
+  const int n_i = max(0, min(64, (keff - u + 15) >> 4));   // my pages: u + 16 i, i < n_i
+  const float* col = &sm.slab[u][t];                       // page u + 16 i sits 16 * kFastTok floats further on
+  // eight loads in flight per step: the loop is bound by shared-memory latency, not by instruction count
+  for (int i0 = 0; i0 < 64; i0 += 8) {
+    if (i0 == 32 && !forced_any && ok) ok = mbar_wait(&sm.full[1], 0, abort_flag);   // pages from 512 on
+    float v[8];
 #pragma unroll
-    for (int j = 0; j < GPT; ++j) {
-      const int k = u + 16 * (i0 + j);
-      if (k < keff) {
-        const float v = sm.slab[k][t];
-        saw_inf |= (v == INFINITY);
-        gm[j] = fmaxf(gm[j], v);           // NaN never wins
-      }
-    }
+    for (int e = 0; e < 8; ++e) v[e] = (i0 + e < n_i) ? col[(i0 + e) * 16 * kFastTok] : -INFINITY;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) gm[(i0 + e) % GPT] = fmaxf(gm[(i0 + e) % GPT], v[e]);   // NaN never wins
   }
+  bool saw_inf = false;
+#pragma unroll
+  for (int j = 0; j < GPT; ++j) saw_inf |= (gm[j] == INFINITY);
 #pragma unroll
   for (int j = 0; j < GPT; ++j) sm.gmax[u + 16 * j][t] = fminf(gm[j], 3.402823466e38f);
   // +inf ranks with FLT_MAX: rewrite such scores in place (rare, CTA-uniform branch)
@@ -451,38 +454,34 @@ topk_select_fast_kernel(const float* __restrict__ ms, int H, int K, int T, int n
   // ---- threshold of each row: the TOPK-th largest of its G group maxima (warp w: rows 2w, 2w + 1) ------------
   for (int rr = 0; rr < 2; ++rr) {
     const int row = warp * 2 + rr;
-    float mine[G / 32];
+    uint32_t gk[G / 32];
 #pragma unroll
-    for (int a = 0; a < G / 32; ++a) mine[a] = sm.gmax[lane + 32 * a][row];
-    int rank[G / 32];
-#pragma unroll
-    for (int a = 0; a < G / 32; ++a) rank[a] = 0;
-    for (int b = 0; b < G; ++b) {
-      const float vb = sm.gmax[b][row];    // broadcast read
-#pragma unroll
-      for (int a = 0; a < G / 32; ++a) {
-        const int ia = lane + 32 * a;
-        rank[a] += (vb > mine[a] || (vb == mine[a] && b < ia)) ? 1 : 0;
-      }
-    }
-#pragma unroll
-    for (int a = 0; a < G / 32; ++a)
-      if (rank[a] == TOPK - 1) sm.thr[row] = mine[a];
+    for (int a = 0; a < G / 32; ++a) gk[a] = ordered_key(sm.gmax[lane + 32 * a][row] + 0.0f);
+    warp_bitonic_sort<G / 32, true>(gk, lane);       // descending
+    const uint32_t tk = __shfl_sync(0xffffffffu, gk[(TOPK - 1) >> 5], (TOPK - 1) & 31);
+    if (lane == 0) sm.thr[row] = key_value(tk);
   }
   __syncthreads();
 
   // ---- B: candidates ------------------------------------------------------------------------------------------
   {
     const float thr = sm.thr[t];
-    for (int i = 0; i < 64; ++i) {
-      const int k = u + 16 * i;
-      if (k < keff) {
-        const float v = sm.slab[k][t];
-        if (v >= thr && v > -INFINITY) {
-          const int slot = atomicAdd(&sm.cnt[t], 1);
-          if (slot < C) {
-            sm.cand_v[t][slot] = v + 0.0f;   // -0.0 -> +0.0
-            sm.cand_k[t][slot] = static_cast<short>(k);
+    for (int i0 = 0; i0 < n_i; i0 += 8) {
+      float v[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = (i0 + e < n_i) ? col[(i0 + e) * 16 * kFastTok] : -INFINITY;
+      bool any = false;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) any |= (v[e] >= thr && v[e] > -INFINITY);
+      if (any) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          if (v[e] >= thr && v[e] > -INFINITY) {
+            const int slot = atomicAdd(&sm.cnt[t], 1);
+            if (slot < C) {
+              sm.cand_v[t][slot] = v[e] + 0.0f;   // -0.0 -> +0.0
+              sm.cand_k[t][slot] = static_cast<short>(u + 16 * (i0 + e));
+            }
           }
         }
       }
@@ -505,7 +504,19 @@ topk_select_fast_kernel(const float* __restrict__ ms, int H, int K, int T, int n
         const float va = a < n ? sm.cand_v[row][a] : 0.f;
         const int ka = a < n ? sm.cand_k[row][a] : 0;
         int rank = 0;
-        for (int b = 0; b < n; ++b) {
+        int b = 0;
+        for (; b + 4 <= n; b += 4) {       // four broadcast reads in flight
+          float vb[4];
+          int kb[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            vb[e] = sm.cand_v[row][b + e];
+            kb[e] = sm.cand_k[row][b + e];
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) rank += (vb[e] > va || (vb[e] == va && kb[e] < ka)) ? 1 : 0;
+        }
+        for (; b < n; ++b) {
           const float vb = sm.cand_v[row][b];
           const int kb = sm.cand_k[row][b];
           rank += (vb > va || (vb == va && kb < ka)) ? 1 : 0;
@@ -572,12 +583,13 @@ topk_select_fast_kernel(const float* __restrict__ ms, int H, int K, int T, int n
     }
     __syncwarp();
   }
+  if (!ok && tid == 0 && status != nullptr) atomicExch(status, MSA_ERR_TIMEOUT);
 }
 
 // [H, K, T] -> [H, K, n_blocks]: max over the tokens of each query block.  A warp owns four consecutive
 // blocks of one (head, page) row and has all their loads in flight before it reduces (one 128-token block is
 // a single 16-byte load per lane, far too little to cover the memory latency on its own).
-constexpr int kBlockMaxPerWarp = 4;
+constexpr int kBlockMaxPerWarp = 8;
 __global__ void block_max_kernel(const float* __restrict__ ms, int K, int T, const int* __restrict__ block_starts,
                                  int n_blocks, float* __restrict__ out) {
   const int warp = (blockIdx.y * blockDim.x + threadIdx.x) >> 5;
@@ -647,8 +659,11 @@ static int launch_topk_fast(const float* ms, int H, int K, int T, int nvp, int f
         cudaFuncSetAttribute(topk_select_fast_kernel<TOPK>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   });
   if (rc != MSA_OK) return rc;
+  CUtensorMap map;
+  const int mrc = make_score_map(&map, ms, H, K, T, kFastTok, 256);
+  if (mrc != MSA_OK) return mrc;
   dim3 grid((T + kFastTok - 1) / kFastTok, H);
-  topk_select_fast_kernel<TOPK><<<grid, 256, smem, st>>>(ms, H, K, T, nvp, fb, fe, out);
+  topk_select_fast_kernel<TOPK><<<grid, 256, smem, st>>>(map, H, K, T, nvp, fb, fe, out, nullptr);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -39,11 +39,69 @@ def _row_map(kv_lens, blk_kv, device):
 
 
 def build_k2q_csr(q2k_indices: torch.Tensor, cu_seqlens_q: torch.Tensor, cu_seqlens_k: torch.Tensor,
-                  blk_kv: int = PAGE):
+                  blk_kv: int = PAGE, **_hints):
     """q2k ``[Hkv, total_q, topK]`` (request-local KV block ids, -1 unused) ->
     ``(k2q_row_ptr[Hkv, total_rows + 1], k2q_q_indices[Hkv, total_q * topK])``:
     for every (KV block, request) row the ascending request-local queries that
-    selected it; unused tail is -1."""
+    selected it; unused tail is -1 (python/fmha_sm100/cute/sparse_index_utils.py:331).
+    CUDA tensors go through ``msa_build_k2q_csr`` (four small kernels, deterministic);
+    CPU tensors through the tensor-op version below.  The reference's size hints
+    (``total_k``, ``max_seqlen_k``, ...) are accepted and not needed."""
+    if q2k_indices.is_cuda:
+        return _build_k2q_csr_device(q2k_indices, cu_seqlens_q, cu_seqlens_k, blk_kv)
+    return _build_k2q_csr_host(q2k_indices, cu_seqlens_q, cu_seqlens_k, blk_kv)
+
+
+_CSR_WORKSPACE_LIMIT = 1 << 30
+
+
+def _build_k2q_csr_device(q2k, cu_seqlens_q, cu_seqlens_k, blk_kv):
+    lib = _lib.get_lib()
+    dev = q2k.device
+    Hkv, total_q, topk = q2k.shape
+    cq = np.asarray(cu_seqlens_q.tolist(), dtype=np.int64)
+    ck = np.asarray(cu_seqlens_k.tolist(), dtype=np.int64)
+    B = len(cq) - 1
+    nblk = ((ck[1:] - ck[:-1]) + blk_kv - 1) // blk_kv
+    rr, rb = _row_map_np((ck[1:] - ck[:-1]).tolist(), blk_kv)
+    total_rows, maxb = int(rr.shape[0]), int(max(1, nblk.max() if B else 1))
+    lut = np.full((max(B, 1), maxb), -1, dtype=np.int32)
+    lut[rr, rb] = np.arange(total_rows, dtype=np.int32)
+    chunk = 256
+    c_req, c_q0, c_len, first = [], [], [], [0]
+    for b in range(B):
+        for s0 in range(int(cq[b]), int(cq[b + 1]), chunk):
+            c_req.append(b)
+            c_q0.append(s0)
+            c_len.append(min(chunk, int(cq[b + 1]) - s0))
+        first.append(len(c_req))
+    n_chunks = len(c_req)
+    ws_bytes = lib.msa_build_k2q_csr_workspace_bytes(Hkv, n_chunks, maxb, total_rows)
+    if ws_bytes > _CSR_WORKSPACE_LIMIT or B == 0:
+        rp, qi = _build_k2q_csr_host(q2k, cu_seqlens_q, cu_seqlens_k, blk_kv)
+        return rp, qi
+    i32 = lambda x: torch.tensor(np.asarray(x, dtype=np.int32), device=dev)  # noqa: E731
+    meta = [i32(c_req), i32(c_q0), i32(c_len), i32(cq), i32(first), i32(nblk), torch.from_numpy(lut).to(dev)]
+    q2k_c = q2k.to(torch.int32).contiguous()
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+    row_ptr = torch.empty(Hkv, total_rows + 1, dtype=torch.int32, device=dev)
+    q_indices = torch.empty(Hkv, total_q * topk, dtype=torch.int32, device=dev)
+    a = _lib.CsrBuildArgs()
+    a.q2k = q2k_c.data_ptr()
+    (a.chunk_request, a.chunk_first_query, a.chunk_len, a.cu_seqlens_q, a.request_first_chunk, a.request_blocks,
+     a.row_of_block) = (m.data_ptr() for m in meta)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    a.row_ptr, a.q_indices = row_ptr.data_ptr(), q_indices.data_ptr()
+    a.total_q, a.q_indices_stride = total_q, total_q * topk
+    a.num_kv_heads, a.topk, a.n_chunks, a.batch, a.max_blocks, a.total_rows = Hkv, topk, n_chunks, B, maxb, total_rows
+    import ctypes
+    _lib.check(lib.msa_build_k2q_csr(ctypes.byref(a), _stream()), "msa_build_k2q_csr")
+    return row_ptr, q_indices
+
+
+def _build_k2q_csr_host(q2k_indices: torch.Tensor, cu_seqlens_q: torch.Tensor, cu_seqlens_k: torch.Tensor,
+                        blk_kv: int = PAGE):
+    """The same index with tensor ops (any device; the CPU tests and the fallback for outsized workspaces)."""
     Hkv, total_q, topk = q2k_indices.shape
     dev = q2k_indices.device
     cq = [int(x) for x in cu_seqlens_q.tolist()]

@@ -460,3 +460,36 @@ def test_mixed_batch_writes_straight_into_caller_buffers():
     assert (out.float().cpu() - ref).abs().max() <= TOL["bf16"]
     msref = O.tile_max_score_paged(q, kp, table, qo, kv, 128)
     assert torch.equal(torch.isfinite(ms.cpu()), torch.isfinite(msref))
+
+
+def test_build_k2q_csr_kernels_match_the_host_builder_and_the_reference_fixture():
+    """msa_build_k2q_csr (count / chunk offsets / row_ptr scan / ordered scatter) == the tensor-op builder on
+    ragged requests with short, empty and full lists; and == the reference's own output on its fixture."""
+    from msa_b200.sparse import _build_k2q_csr_host
+    z = np.load(os.path.join(G, "k2q_csr.npz"))
+    q2k = torch.from_numpy(z["q2k"])
+    cu_q, cu_k = torch.from_numpy(z["cu_q"]), torch.from_numpy(z["cu_k"])
+    rp, qi = msa_b200.build_k2q_csr(q2k.cuda(), cu_q.cuda(), cu_k.cuda(), 128)
+    assert torch.equal(rp.cpu(), torch.from_numpy(z["row_ptr"])) and torch.equal(qi.cpu(), torch.from_numpy(z["q_indices"]))
+    g = torch.Generator().manual_seed(9)
+    qo, kv, Hkv, topk = [700, 0, 33, 1500], [5000, 128, 300, 20000], 3, 8
+    T = sum(qo)
+    q2k = torch.full((Hkv, T, topk), -1, dtype=torch.int32)
+    t = 0
+    for ql, kl in zip(qo, kv):
+        npg = (kl + 127) // 128
+        for i in range(ql):
+            for h in range(Hkv):
+                n = int(torch.randint(0, min(topk, npg) + 1, (1,), generator=g))
+                # popular first block + random others: long rows and short rows
+                pick = torch.randperm(npg, generator=g)[:n]
+                if n > 0 and i % 3:
+                    pick[0] = 0
+                u = torch.unique(pick).int()            # ascending, distinct (the forced block may repeat one)
+                q2k[h, t, :u.numel()] = u
+            t += 1
+    cu_q = torch.tensor([0] + list(np.cumsum(qo)), dtype=torch.int32)
+    cu_k = torch.tensor([0] + list(np.cumsum(kv)), dtype=torch.int32)
+    rp_h, qi_h = _build_k2q_csr_host(q2k, cu_q, cu_k, 128)
+    rp_d, qi_d = msa_b200.build_k2q_csr(q2k.cuda(), cu_q.cuda(), cu_k.cuda(), 128)
+    assert torch.equal(rp_d.cpu(), rp_h) and torch.equal(qi_d.cpu(), qi_h)
