@@ -255,7 +255,7 @@ def _csr_plan(q, k, topK, cu_seqlens_q, cu_seqlens_k, blk_kv, causal, page_table
 
 def _csr_forward(q, k, v, k2q_row_ptr, k2q_q_indices, topK, cu_seqlens_q, cu_seqlens_k, blk_kv, causal,
                  softmax_scale, return_softmax_lse, page_table, seqused_k, kv_dtype, qk_scale, v_scale,
-                 k_sf=None, v_sf=None, usable_SM_count=-1):
+                 k_sf=None, v_sf=None, usable_SM_count=-1, lse_temperature_scale=1.0, return_temperature_lse=False):
     if blk_kv != PAGE:
         raise MsaError(f"blk_kv must be {PAGE}")
     if topK not in (4, 8, 16, 32, 64):
@@ -272,8 +272,18 @@ def _csr_forward(q, k, v, k2q_row_ptr, k2q_q_indices, topK, cu_seqlens_q, cu_seq
     out = torch.empty(q.shape[0], Hq, 128, dtype=torch.bfloat16, device=q.device)
     lse = torch.empty(q.shape[0], Hq, dtype=torch.float32, device=q.device) if return_softmax_lse else None
     qq = q.to(torch.bfloat16).contiguous() if q.dtype != torch.bfloat16 else q.contiguous()
-    _run_prefill(qq, k.contiguous(), v.contiguous(), plan, ent["kv_indices"], q2k, plan["qo_offset"], out, None, lse,
+    kc, vc = k.contiguous(), v.contiguous()
+    _run_prefill(qq, kc, vc, plan, ent["kv_indices"], q2k, plan["qo_offset"], out, None, lse,
                  softmax_scale, qk_scale, v_scale, kv_dtype, paged, k_sf, v_sf)
+    if return_temperature_lse:
+        # LSE of the logits scaled by softmax_scale / lse_temperature_scale (python/fmha_sm100/cute/interface.py:
+        # 665-699): a second pass of the same kernel at that scale, whose LSE is kept and whose output is dropped --
+        # the price of an output few callers ask for, instead of a second exponential per score in every call
+        lse_t = torch.empty_like(lse)
+        scratch = torch.empty_like(out)
+        _run_prefill(qq, kc, vc, plan, ent["kv_indices"], q2k, plan["qo_offset"], scratch, None, lse_t,
+                     softmax_scale / lse_temperature_scale, qk_scale, v_scale, kv_dtype, paged, k_sf, v_sf)
+        return out, lse, lse_t
     return (out, lse) if return_softmax_lse else out
 
 
@@ -292,14 +302,18 @@ def sparse_atten_func(q, k, v, k2q_row_ptr, k2q_q_indices, topK, *, cu_seqlens_q
     effect here: nothing is split, accumulation is fp32 in TMEM."""
     if softmax_scale is None:
         softmax_scale = q.shape[-1] ** -0.5
-    if return_temperature_lse:
-        raise MsaError("temperature LSE is not implemented")
+    lse_temperature_scale = float(lse_temperature_scale)
+    if not math.isfinite(lse_temperature_scale) or lse_temperature_scale <= 0.0:
+        raise ValueError(f"lse_temperature_scale must be finite and > 0, got {lse_temperature_scale}")
+    if return_temperature_lse and not return_softmax_lse:
+        raise ValueError("return_temperature_lse=True requires return_softmax_lse=True")
     if cu_seqlens_q is None or cu_seqlens_k is None:
         raise ValueError("sparse_atten_func requires CSR varlen metadata: pass cu_seqlens_q and cu_seqlens_k")
     kv_dtype = _lib.MSA_KV_FP8_E4M3 if k.dtype == torch.float8_e4m3fn else _lib.MSA_KV_BF16
     return _csr_forward(q, k, v, k2q_row_ptr, k2q_q_indices, int(topK), cu_seqlens_q, cu_seqlens_k, int(blk_kv),
                         bool(causal), float(softmax_scale), bool(return_softmax_lse), page_table, seqused_k,
-                        kv_dtype, 1.0, 1.0, usable_SM_count=int(usable_SM_count))
+                        kv_dtype, 1.0, 1.0, usable_SM_count=int(usable_SM_count),
+                        lse_temperature_scale=lse_temperature_scale, return_temperature_lse=bool(return_temperature_lse))
 
 
 def sparse_atten_nvfp4_kv_func(q, k, v, k_scale_128x4, v_scale_128x4, k_global_scale, v_global_scale, k2q_row_ptr,
@@ -321,7 +335,9 @@ def sparse_atten_nvfp4_kv_func(q, k, v, k_scale_128x4, v_scale_128x4, k_global_s
     return _csr_forward(q, k.view(torch.uint8), v.view(torch.uint8), k2q_row_ptr, k2q_q_indices, int(topK),
                         cu_seqlens_q, cu_seqlens_k, int(blk_kv), bool(causal), float(softmax_scale),
                         bool(return_softmax_lse), page_table, seqused_k, _lib.MSA_KV_NVFP4, kg, vg,
-                        k_scale_128x4.view(torch.uint8).contiguous(), v_scale_128x4.view(torch.uint8).contiguous())
+                        k_scale_128x4.view(torch.uint8).contiguous(), v_scale_128x4.view(torch.uint8).contiguous(),
+                        lse_temperature_scale=float(lse_temperature_scale),
+                        return_temperature_lse=bool(return_temperature_lse))
 
 
 def sparse_prefill_nvfp4(q, k_q, v_q, plan_info, kv_indices, kv_block_indexes, sm_scale=None, return_lse=False):

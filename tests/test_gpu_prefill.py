@@ -493,3 +493,31 @@ def test_build_k2q_csr_kernels_match_the_host_builder_and_the_reference_fixture(
     rp_h, qi_h = _build_k2q_csr_host(q2k, cu_q, cu_k, 128)
     rp_d, qi_d = msa_b200.build_k2q_csr(q2k.cuda(), cu_q.cuda(), cu_k.cuda(), 128)
     assert torch.equal(rp_d.cpu(), rp_h) and torch.equal(qi_d.cpu(), qi_h)
+
+
+def test_sparse_atten_func_temperature_lse():
+    """return_temperature_lse: the LSE of the logits at softmax_scale / lse_temperature_scale
+    (python/fmha_sm100/cute/interface.py:665-699), next to the ordinary output and LSE."""
+    qo, kv, Hq, Hkv, topk = [200, 90], [1000, 640], 4, 2, 4
+    q, kp, vp, table, idx = _sparse_case(qo, kv, Hq, Hkv, topk, "bf16", "token", seed=61)
+    cu_q, cu_k, rp, qi = _csr_inputs(qo, kv, idx)
+    ind = O.page_indptr(kv)
+    pt = torch.zeros(2, 8, dtype=torch.int32)
+    for b in range(2):
+        pt[b, :ind[b + 1] - ind[b]] = table[ind[b]:ind[b + 1]]
+    cu_k_cap = torch.tensor([0, 1024, 2048], dtype=torch.int32)
+    rp, qi = msa_b200.build_k2q_csr(idx.permute(1, 0, 2).contiguous().cuda(), cu_q.cuda(), cu_k_cap.cuda(), 128)
+    out, lse, lse_t = msa_b200.sparse_atten_func(
+        q.cuda(), kp.cuda(), vp.cuda(), rp, qi, topk, cu_seqlens_q=cu_q.cuda(), cu_seqlens_k=cu_k_cap.cuda(),
+        max_seqlen_q=max(qo), max_seqlen_k=max(kv), causal=True, return_softmax_lse=True, return_temperature_lse=True,
+        lse_temperature_scale=2.5, page_table=pt.cuda(), seqused_k=torch.tensor(kv, dtype=torch.int32).cuda())
+    ref, lse_ref = O.sparse_attention_paged(q, kp, vp, table, qo, kv, idx)
+    _, lse_t_ref = O.sparse_attention_paged(q, kp, vp, table, qo, kv, idx, sm_scale=128 ** -0.5 / 2.5)
+    assert (out.float().cpu() - ref).abs().max() <= TOL["bf16"]
+    fin = torch.isfinite(lse_ref)
+    assert torch.allclose(lse.cpu()[fin], lse_ref[fin], atol=2e-2, rtol=1e-3)
+    assert torch.allclose(lse_t.cpu()[fin], lse_t_ref[fin], atol=2e-2, rtol=1e-3)
+    with pytest.raises(ValueError):
+        msa_b200.sparse_atten_func(q.cuda(), kp.cuda(), vp.cuda(), rp, qi, topk, cu_seqlens_q=cu_q.cuda(),
+                                   cu_seqlens_k=cu_k_cap.cuda(), max_seqlen_q=max(qo), max_seqlen_k=max(kv),
+                                   causal=True, return_temperature_lse=True, page_table=pt.cuda())
