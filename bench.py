@@ -638,7 +638,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="skip stages / decode / e2e (profiling runs)")
-    ap.add_argument("--stage", default="prefill", choices=["prefill", "decode", "topk", "kvappend", "reference_sm100"],
+    ap.add_argument("--stage", default="prefill", choices=["prefill", "decode", "topk", "proxy", "kvappend", "reference_sm100"],
                     help="profiling runs: time only this stage and print a short JSON line")
     ap.add_argument("--ref-kv", default="both", choices=["both", "fp8", "nvfp4"],
                     help="--stage reference_sm100: which K/V format to run")
@@ -701,6 +701,13 @@ def main():
             except Exception as e:  # the reference failed to import, compile or launch on this box
                 out[which] = {"unavailable": f"{type(e).__name__}: {str(e).splitlines()[0] if str(e) else ''}"[:300]}
         print(json.dumps(out), flush=True)
+        return
+    if args.stage == "proxy":
+        w = build_prefill_workload(dev, seed=2, lens=lens)
+        mp, _ = time_fn(w["stage1"], args.steps, args.warmup)
+        pairs = sum(L * (L + 1) / 2 for L in lens)
+        print(json.dumps({"stage": "proxy", "lens": list(lens), "ms": mp,
+                          "tflops_64dim_1head": pairs * 64 * 2 / (mp * 1e-3) / 1e12}), flush=True)
         return
     if args.stage == "kvappend":
         ka = build_kv_append(dev, tokens=sum(lens))
