@@ -70,6 +70,10 @@ typedef struct msa_plan_desc {
   int32_t num_sms;          /* SMs the decode split choice may assume (usable_SM_count), <= 0 = 148 */
   int32_t tile_rows;        /* query rows per work entry: 0 or 128, or 256 for the paired-tile score-only pass
                                (msa_fmha_args.tile_rows) */
+  int32_t dense_kv_splits;  /* > 1: every query tile becomes this many work entries, each over a contiguous range of
+                               the tile's visible pages, writing output rows split * total_q + token (merged by
+                               msa_fmha_combine); for dense calls whose query tiles alone cannot fill the GPU.
+                               0 or 1: one entry per tile */
 } msa_plan_desc;
 
 /* Sizes of the arrays msa_plan fills: query tiles, total query tokens, total page-table slots. */
@@ -140,9 +144,15 @@ typedef struct msa_fmha_args {
   float* max_score;       /* float32 [num_qo_heads, max_k_tiles, total_q] raw q.k tile maxima, or NULL.
                              Only tiles the kernel visits are written; the caller pre-fills -inf. */
   const int32_t* work;    /* int32 [n_work, 8], one entry per 128-row query tile, heaviest first:
-                             {request, first token (global), valid rows <= 128, first token (request-local),
+                             {request, first token (global), valid rows <= 128 | first page << 10,
+                              first token (request-local),
                               kv_len, causal offset (row i sees key j iff i + offset >= j),
-                              first page-table slot of the request (paged) | first K/V token (ragged), 0}.
+                              first page-table slot of the request (paged) | first K/V token (ragged),
+                              output row offset}.
+                             "first page" and "output row offset" are 0 unless the list was planned with
+                             dense_kv_splits > 1: an entry then covers the pages [first page, ceil(kv_len / 128))
+                             of a dense request (kv_len cut at the end of the entry's page range) and writes its
+                             output / LSE rows at token + output row offset.
                              With page lists (kv_block_indexes != NULL) kv_len is at most 16384 pages
                              (2 097 152 keys); a longer request is skipped (zero output) and the status word
                              receives MSA_ERR_UNSUPPORTED. */
@@ -178,9 +188,20 @@ typedef struct msa_fmha_args {
   int64_t max_score_head_stride; /* elements between consecutive heads; 0 = max_k_tiles * tile stride.  The two
                                     strides let a call write its tokens into a slice [.., .., t0:t1] of a larger
                                     score tensor (the decode and prefill halves of a mixed batch) */
+  int64_t out_rows;              /* rows of out / lse; 0 = total_q.  dense_kv_splits * total_q when the work list
+                                    was planned with KV splits: out and lse are then the partial buffers that
+                                    msa_fmha_combine merges (lse must be given) */
 } msa_fmha_args;
 
 int msa_fmha_fwd(const msa_fmha_args* args, void* stream);
+
+/* Merges the partial results of a call planned with msa_plan_desc.dense_kv_splits = n_splits (the role of the
+ * combine step behind num_kv_splits in python/fmha_sm100/api.py:944-1026):
+ *   out[t, h, :] = sum_s exp(lse_s[t, h] - lse[t, h]) * partial_out[s, t, h, :],  lse = log sum_s exp(lse_s)
+ * partial_out bf16 [n_splits, total_q, num_qo_heads, 128], partial_lse float32 [n_splits, total_q, num_qo_heads]
+ * (natural log, -inf where a split saw no key); out bf16 [total_q, num_qo_heads, 128]; lse float32 or NULL. */
+int msa_fmha_combine(const void* partial_out, const float* partial_lse, int32_t n_splits, int64_t total_q,
+                     int32_t num_qo_heads, void* out, float* lse, void* stream);
 
 /* Optional pre-pass for page-list calls: flags[w * list_heads + h] = 1 iff every row of query tile `w` (an entry of
  * `work`) has the same list for list head `h`.  MSA selects pages per query block, so the per-token lists of the

@@ -21,7 +21,7 @@ SOURCES = ["abi.cu", "topk.cu", "decode.cu", "fmha_host.cu", "kv_quant.cu", "pla
 
 MSA_KV_BF16, MSA_KV_FP8_E4M3, MSA_KV_NVFP4 = 0, 1, 2
 MSA_ERR_TIMEOUT = -3
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 
 class MsaError(RuntimeError):
@@ -42,6 +42,7 @@ class FmhaArgs(Structure):
         ("sm_scale", c_float), ("qk_scale", c_float), ("v_scale", c_float),
         ("status", c_void_p), ("max_ctas", c_int32), ("qk_dim", c_int32),
         ("tile_rows", c_int32), ("tile_uniform", c_void_p), ("max_score_tile_stride", c_int64), ("max_score_head_stride", c_int64),
+        ("out_rows", c_int64),
     ]
 
 
@@ -73,6 +74,7 @@ class PlanDesc(Structure):
         ("batch", c_int32), ("qo_lens", c_void_p), ("kv_lens", c_void_p), ("qo_offset", c_void_p),
         ("causal", c_int32), ("paged", c_int32), ("num_qo_heads", c_int32), ("num_kv_heads", c_int32),
         ("kv_block_num", c_int32), ("num_kv_splits", c_int32), ("num_sms", c_int32), ("tile_rows", c_int32),
+        ("dense_kv_splits", c_int32),
     ]
 
 
@@ -164,6 +166,8 @@ def _bind(lib):
     lib.msa_topk_select.argtypes = [vp, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, vp, vp]
     lib.msa_block_max.restype = c_int32
     lib.msa_block_max.argtypes = [vp, c_int32, c_int32, c_int32, vp, c_int32, vp, vp]
+    lib.msa_fmha_combine.restype = c_int32
+    lib.msa_fmha_combine.argtypes = [vp, vp, c_int32, c_int64, c_int32, vp, vp, vp]
     lib.msa_list_uniformity.restype = c_int32
     lib.msa_list_uniformity.argtypes = [vp, c_int32, vp, c_int32, c_int32, vp, vp]
     lib.msa_fmha_fwd.restype = c_int32

@@ -63,7 +63,7 @@ def _np_ptr(a: Optional[np.ndarray]):
 
 def _host_plan(qo_lens, kv_lens, qo_offset, causal: bool, paged: bool, num_qo_heads: int = 1, num_kv_heads: int = 1,
                kv_block_num: int = -1, num_kv_splits: int = -1, num_sms: int = 0, decode: bool = False,
-               tile_rows: int = 128):
+               tile_rows: int = 128, dense_kv_splits: int = 0):
     """Runs ``msa_plan`` (the host planner of libmsa_b200.so, standing in for
     csrc/fmha_sm100_plan.cu:18-35 and csrc/include/plan.cuh:899-1054 of the reference) and
     returns host arrays: ``(work[n_work, 8], kv_page_indptr[B + 1], token_request, token_pos, num_splits)``;
@@ -78,6 +78,7 @@ def _host_plan(qo_lens, kv_lens, qo_offset, causal: bool, paged: bool, num_qo_he
     d.num_qo_heads, d.num_kv_heads = int(num_qo_heads), int(num_kv_heads)
     d.kv_block_num, d.num_kv_splits, d.num_sms = int(kv_block_num), int(num_kv_splits or -1), int(num_sms)
     d.tile_rows = int(tile_rows)
+    d.dense_kv_splits = int(dense_kv_splits)
     n_work, total_q, total_pages = ctypes.c_int32(0), ctypes.c_int64(0), ctypes.c_int64(0)
     check(lib.msa_plan_sizes(ctypes.byref(d), ctypes.byref(n_work), ctypes.byref(total_q), ctypes.byref(total_pages)),
           "msa_plan_sizes")
@@ -190,6 +191,24 @@ def _fmha_sm100_plan(
         # of one head on a CTA instead of two heads: 256-row work entries
         work2 = _host_plan(qo_lens, kv_lens, off, causal, page_size > 0, num_qo_heads, num_kv_heads, tile_rows=256)[0]
         plan["work_pair"] = torch.from_numpy(work2).to(device).contiguous()
+    plan["dense_kv_splits"] = 1
+    if not sparse and total_q > 0 and work.shape[0] > 0:
+        # A dense call with few query tiles (a short query over a long context) cannot fill the GPU with one
+        # CTA per (tile, head pair): each tile is split over ranges of its pages and the partial results are
+        # merged afterwards (the role num_kv_splits has in python/fmha_sm100/api.py:944-1026).
+        hr = num_qo_heads // num_kv_heads
+        items = int(work.shape[0]) * (num_qo_heads // (2 if hr % 2 == 0 else 1))
+        max_pages = max((min(kl, max(0, ql + o)) if causal else kl) for ql, kl, o in zip(qo_lens, kv_lens, off))
+        max_pages = (max(0, max_pages) + PAGE - 1) // PAGE
+        if num_kv_splits is not None and num_kv_splits >= 1:
+            n_split = min(int(num_kv_splits), max(1, max_pages))     # forced; 1 = never split
+        else:
+            n_split = min(sms // max(1, items), max_pages // 8, 64)
+        if n_split > 1:
+            work_s = _host_plan(qo_lens, kv_lens, off, causal, page_size > 0, num_qo_heads, num_kv_heads,
+                                dense_kv_splits=n_split)[0]
+            plan["work_split"] = torch.from_numpy(work_s).to(device).contiguous()
+            plan["dense_kv_splits"] = n_split
     plan["status"] = torch.zeros(1, dtype=torch.int32, device=device)
     plan["use_decode_kernel"] = bool(use_decode)
     plan["pack_factor"] = 1
@@ -299,6 +318,20 @@ def _run_prefill(q, k, v, plan, kv_indices, kv_block_indexes, qo_offset_t, out, 
     a.out, a.lse, a.max_score = _ptr(out), _ptr(lse), _ptr(max_score)
     pair = out is None and kv_block_indexes is None and "work_pair" in plan
     work = plan["work_pair"] if pair else plan["work"]
+    n_split = 1
+    if (out is not None and kv_block_indexes is None and "work_split" in plan
+            and qo_offset_t is plan["qo_offset"]):
+        # KV splits of a short dense call: every split writes a normalised partial and its LSE into buffers the
+        # plan keeps, msa_fmha_combine merges them into out / lse
+        work, n_split = plan["work_split"], plan["dense_kv_splits"]
+        final_out, final_lse = out, lse
+        if "split_out" not in plan:
+            plan["split_out"] = torch.empty(n_split * q.shape[0], q.shape[1], HEAD_DIM, dtype=torch.bfloat16,
+                                            device=q.device)
+            plan["split_lse"] = torch.empty(n_split * q.shape[0], q.shape[1], dtype=torch.float32, device=q.device)
+        out, lse = plan["split_out"], plan["split_lse"]
+        a.out, a.lse = _ptr(out), _ptr(lse)
+        a.out_rows = int(out.shape[0])
     if qo_offset_t is not plan["qo_offset"]:
         # runtime causal-offset override: patch column 5 of a copy of the work list
         work = work.clone()
@@ -336,6 +369,9 @@ def _run_prefill(q, k, v, plan, kv_indices, kv_block_indexes, qo_offset_t, out, 
     a.status = _ptr(plan["status"])
     a.max_ctas = max(0, int(plan.get("usable_SM_count", -1)))
     check(lib.msa_fmha_fwd(ctypes.byref(a), _stream()), "msa_fmha_fwd")
+    if n_split > 1:
+        check(lib.msa_fmha_combine(_ptr(out), _ptr(lse), n_split, int(q.shape[0]), int(q.shape[1]), _ptr(final_out),
+                                   _ptr(final_lse), _stream()), "msa_fmha_combine")
 
 
 def _run_decode(q, k, v, plan, kv_indices, kv_block_indexes, out, lse, sm_scale, qk_scale, v_scale,

@@ -3,7 +3,7 @@
 
 extern "C" {
 
-int msa_abi_version(void) { return 2; }
+int msa_abi_version(void) { return 3; }
 
 const char* msa_error_string(int code) {
   switch (code) {
@@ -75,6 +75,12 @@ int msa_list_uniformity(const int32_t* work, int32_t n_work, const int32_t* kv_b
 
 int msa_fmha_fwd(const msa_fmha_args* args, void* stream) {
   return msa::fmha_fwd(args, static_cast<cudaStream_t>(stream));
+}
+
+int msa_fmha_combine(const void* partial_out, const float* partial_lse, int32_t n_splits, int64_t total_q,
+                     int32_t num_qo_heads, void* out, float* lse, void* stream) {
+  return msa::fmha_combine(partial_out, partial_lse, n_splits, total_q, num_qo_heads, out, lse,
+                           static_cast<cudaStream_t>(stream));
 }
 
 size_t msa_decode_workspace_bytes(int32_t num_tokens, int32_t num_qo_heads, int32_t num_splits) {

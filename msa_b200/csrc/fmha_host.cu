@@ -148,7 +148,9 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
   if (a->max_score_tile_stride > 0 && a->max_score_tile_stride < a->total_q) return MSA_ERR_INVALID;
   if (a->qk_dim != 0 && a->qk_dim != 64 && a->qk_dim != 128) return MSA_ERR_INVALID;
   if (a->qk_dim == 64 && (a->out != nullptr || a->kv_dtype == MSA_KV_NVFP4)) return MSA_ERR_UNSUPPORTED;
+  if (a->out_rows != 0 && (a->out_rows < a->total_q || a->out == nullptr || a->lse == nullptr)) return MSA_ERR_INVALID;
   if (a->n_work <= 0 || a->total_q <= 0) return MSA_OK;
+  const int64_t out_rows = a->out_rows > 0 ? a->out_rows : a->total_q;
 
   FmhaParams p{};
   p.out = static_cast<__nv_bfloat16*>(a->out);
@@ -204,7 +206,7 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
   int rc = make_q_map(&mq, a->q, a->total_q, p.Hq);
   if (rc != MSA_OK) return rc;
   // score-only calls have no output: the map is never used then, but must be a valid one
-  rc = make_o_map(&mo, a->out != nullptr ? a->out : a->q, a->total_q, p.Hq);
+  rc = make_o_map(&mo, a->out != nullptr ? a->out : a->q, a->out != nullptr ? out_rows : a->total_q, p.Hq);
   if (rc != MSA_OK) return rc;
   if (a->kv_dtype == MSA_KV_NVFP4) {
     mk = mq;  // pages are fetched with untiled bulk copies
@@ -228,6 +230,62 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
 }
 
 // ---------------------------------------------------------------------------
+// Merge of KV splits: a dense call with few query tiles is planned as n_splits work entries per tile, each over a
+// range of the pages; every split leaves a normalised bf16 partial and its natural-log LSE.  One warp per
+// (token, head) row: lane l owns columns 4l .. 4l + 3.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) fmha_combine_kernel(const uint2* __restrict__ part_o, const float* __restrict__ part_lse,
+                                                          int n_splits, long long n_rows, uint2* __restrict__ out,
+                                                          float* __restrict__ lse) {
+  const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= n_rows) return;
+  float m = -INFINITY;
+  for (int s = lane; s < n_splits; s += 32) m = fmaxf(m, __ldg(part_lse + s * n_rows + row));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  float wsum = 0.f;
+  if (m > -INFINITY) {
+    for (int s = 0; s < n_splits; ++s) {
+      const float l = __ldg(part_lse + s * n_rows + row);
+      if (l == -INFINITY) continue;
+      const float w = __expf(l - m);
+      const uint2 v = __ldg(part_o + (s * n_rows + row) * 32 + lane);
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+      acc[0] += w * a.x;
+      acc[1] += w * a.y;
+      acc[2] += w * b.x;
+      acc[3] += w * b.y;
+      wsum += w;
+    }
+  }
+  const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+  uint2 r;
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(acc[0] * inv, acc[1] * inv);
+  const __nv_bfloat162 hi = __floats2bfloat162_rn(acc[2] * inv, acc[3] * inv);
+  r.x = *reinterpret_cast<const uint32_t*>(&lo);
+  r.y = *reinterpret_cast<const uint32_t*>(&hi);
+  out[row * 32 + lane] = r;
+  if (lse != nullptr && lane == 0) lse[row] = wsum > 0.f ? m + logf(wsum) : -INFINITY;
+}
+
+int fmha_combine(const void* partial_out, const float* partial_lse, int n_splits, int64_t total_q, int num_qo_heads,
+                 void* out, float* lse, cudaStream_t st) {
+  if (partial_out == nullptr || partial_lse == nullptr || out == nullptr || n_splits <= 0 || num_qo_heads <= 0 ||
+      total_q < 0)
+    return MSA_ERR_INVALID;
+  const long long n_rows = static_cast<long long>(total_q) * num_qo_heads;
+  if (n_rows == 0) return MSA_OK;
+  const long long blocks = (n_rows * 32 + 255) / 256;
+  if (blocks > 0x7fffffffLL) return MSA_ERR_TOO_LARGE;
+  fmha_combine_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(static_cast<const uint2*>(partial_out), partial_lse,
+                                                                    n_splits, n_rows, static_cast<uint2*>(out), lse);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------
 // Which query tiles have one page list for all their rows?  MSA selects pages per query block, so the per-token
 // lists the API takes are usually 128 copies of one row; the attention kernel then builds a tile's page bitmap
 // from a single row instead of 128.  One CTA per (tile, list head): row r is compared with row 0.
@@ -240,7 +298,7 @@ __global__ void __launch_bounds__(128) list_uniform_kernel(const int4* __restric
   const int* row0 = lists + (static_cast<size_t>(w.y) * list_heads + lh) * topk;
   const int* mine = lists + (static_cast<size_t>(w.y + r) * list_heads + lh) * topk;
   int same = 1;
-  if (r > 0 && r < w.z) {
+  if (r > 0 && r < (w.z & 1023)) {
     if ((topk & 3) == 0) {
       for (int e = 0; e < topk; e += 4) {
         const int4 a = __ldg(reinterpret_cast<const int4*>(row0 + e)), b = __ldg(reinterpret_cast<const int4*>(mine + e));

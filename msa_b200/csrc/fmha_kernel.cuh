@@ -171,14 +171,16 @@ struct PageWalk {
   uint32_t bits;
   int w;
   int sparse;
-  __device__ __forceinline__ void init(int is_sparse, const uint32_t* bitmap, int n_pages) {
+  int lo;   // dense walk: first page of the range (a KV split of a short-query call starts above page 0)
+  __device__ __forceinline__ void init(int is_sparse, const uint32_t* bitmap, int n_pages, int first_page = 0) {
     sparse = is_sparse;
     bm = bitmap;
     bits = 0;
+    lo = first_page;
     w = is_sparse ? (n_pages + 31) >> 5 : n_pages;
   }
   __device__ __forceinline__ int next() {
-    if (!sparse) return --w;  // n-1 ... 0, then negative
+    if (!sparse) return --w >= 0 ? w + lo : -1;  // lo + n-1 ... lo, then -1
     while (bits == 0) {
       if (--w < 0) return -1;
       bits = bm[w];
@@ -199,16 +201,23 @@ struct PageWalk {
 // What every role needs to know about one work item.
 struct ItemInfo {
   int req, tok0, rows, qloc0, h0, g, kv_len, qo_off, kv_base, n_pages_req, walk_n;
+  int page_lo;   // dense walk starts at this page (KV splits of short-query calls), else 0
+  int out_off;   // added to the token index of output / LSE rows (split s writes rows s * total_q + token)
   bool oversize;
 };
 
 // w, w2: the two int4 halves of the item's work record
+// SPLITS: the work list may carry KV splits (dense calls with output only); elsewhere the two fields are constants,
+// so that the kernels of the other modes carry no trace of them.
+template <bool SPLITS>
 __device__ __forceinline__ ItemInfo decode_item(const FmhaParams& p, int item, int nt, const int4 w, const int4 w2) {
   ItemInfo it;
   const int hg = item % p.n_head_groups;  // head group fastest: CTAs running side by side share K/V pages
   it.req = w.x;
   it.tok0 = w.y;
-  it.rows = w.z;
+  it.rows = SPLITS ? (w.z & 1023) : w.z;     // rows | first page << 10
+  it.page_lo = SPLITS ? (w.z >> 10) : 0;
+  it.out_off = SPLITS ? w2.w : 0;
   it.qloc0 = w.w;
   it.h0 = p.pair_tiles ? hg : hg * nt;
   it.g = it.h0 / p.hr;
@@ -223,12 +232,13 @@ __device__ __forceinline__ ItemInfo decode_item(const FmhaParams& p, int item, i
   int kv_vis = it.kv_len;  // keys visible to the last row of the tile bound the dense walk
   if (p.causal) kv_vis = min(it.kv_len, it.qloc0 + it.rows + it.qo_off);
   const int n_dense = kv_vis > 0 ? (kv_vis + 127) >> 7 : 0;
-  it.walk_n = p.sparse ? it.n_pages_req : n_dense;
+  it.walk_n = p.sparse ? it.n_pages_req : (SPLITS ? max(0, n_dense - it.page_lo) : n_dense);
   return it;
 }
+template <bool SPLITS>
 __device__ __forceinline__ ItemInfo load_item(const FmhaParams& p, int item, int nt) {
   const int wi = item / p.n_head_groups;
-  return decode_item(p, item, nt, __ldg(p.work + 2 * wi), __ldg(p.work + 2 * wi + 1));
+  return decode_item<SPLITS>(p, item, nt, __ldg(p.work + 2 * wi), __ldg(p.work + 2 * wi + 1));
 }
 
 // Calls f(entry index, page) for the leading valid entries of one page list (ascending ids, -1 tail):
@@ -387,6 +397,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   using Smem = FmhaSmem<NT, KVMODE>;
   constexpr int NK = Cfg::kKStages, NV = Cfg::kVStages, NKS = Cfg::kKStagesScore;
   constexpr bool kDoPv = !SCORE;
+  constexpr bool kSplits = !SCORE && LISTS == 0;   // only dense calls with output are ever planned with KV splits
   const bool sparse = LISTS != 0 && p.sparse != 0;
   const bool pair_tiles = SCORE && p.pair_tiles != 0;
   constexpr int NRAW = Cfg::kRawStages > 0 ? Cfg::kRawStages : 1;
@@ -517,9 +528,9 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       if (sparse) {
         // the producer published the item's work record (and a uniform tile's list cursor) with the bitmap
         ok = ok && mbar_wait(&sm.bm_full[nx.bm], (j >> 1) & 1, abort_flag);
-        nx.info = decode_item(p, item, NT, sm.item_work[nx.bm][0], sm.item_work[nx.bm][1]);
+        nx.info = decode_item<kSplits>(p, item, NT, sm.item_work[nx.bm][0], sm.item_work[nx.bm][1]);
       } else {
-        nx.info = load_item(p, item, NT);
+        nx.info = load_item<kSplits>(p, item, NT);
       }
       const int r_tile = pair_tiles ? t * 128 + r : r;   // my row within the work entry
       nx.row_valid = r_tile < nx.info.rows;
@@ -555,7 +566,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           nx.prev_page = prev_page;
         }
       }
-      nx.walk.init(sparse, sm.bitmap[nx.bm], nx.info.walk_n);
+      nx.walk.init(sparse, sm.bitmap[nx.bm], nx.info.walk_n, kSplits ? nx.info.page_lo : 0);
       nx.first_page = ok ? nx.walk.next() : -1;
       if (nx.first_page >= 0) {
         if constexpr (Cfg::kQConvert) {
@@ -856,7 +867,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       pend.m_used = m_used;
       pend.l_sum = l_sum;
       pend.sl2 = sl2;
-      pend.tok = tok;
+      pend.tok = kSplits ? tok + info.out_off : tok;
       pend.h = h;
       pend.n_iter = n_iter;
       pend.row_valid = row_valid;
@@ -895,7 +906,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const int b = jj & 1;
         const int wi = item / p.n_head_groups;
         const int4 w = __ldg(p.work + 2 * wi), w2 = __ldg(p.work + 2 * wi + 1);
-        const ItemInfo info = decode_item(p, item, NT, w, w2);
+        const ItemInfo info = decode_item<kSplits>(p, item, NT, w, w2);
         const int lh = (p.list_heads == p.Hkv) ? info.g : info.h0;
         const bool uniform = p.tile_uniform != nullptr &&
                              __ldg(p.tile_uniform + static_cast<size_t>(wi) * p.list_heads + lh) != 0;
@@ -968,13 +979,13 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         if (item < 0) break;
         if (lane == 0) { MSA_TRACE(11, pg_total, clock64()) }
         const int b = j & 1;
-        const ItemInfo info = sparse ? decode_item(p, item, NT, sm.item_work[b][0], sm.item_work[b][1])
-                                       : load_item(p, item, NT);
+        const ItemInfo info = sparse ? decode_item<kSplits>(p, item, NT, sm.item_work[b][0], sm.item_work[b][1])
+                                       : load_item<kSplits>(p, item, NT);
         const int next_item = item_of(j + 1);
         bool next_pending = sparse && next_item >= 0;
         if (lane == 0) { MSA_TRACE(12, pg_total, clock64()) }
         PageWalk walk;
-        walk.init(sparse, sm.bitmap[b], info.walk_n);
+        walk.init(sparse, sm.bitmap[b], info.walk_n, kSplits ? info.page_lo : 0);
         int page = walk.next();
         if (page >= 0) {
           // Q of this item: the tile buffer is free once the previous item's last QK has completed
@@ -1110,7 +1121,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           if (!ok) break;
           count = sm.item_pages[b];
         } else {
-          count = load_item(p, item, NT).walk_n;
+          count = load_item<kSplits>(p, item, NT).walk_n;
         }
         if (count > 0) {
           MSA_TBEGIN
@@ -1269,7 +1280,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         for (int j = 0; ok; ++j) {
           const int item = item_of(j);
           if (item < 0) break;
-          const ItemInfo info = load_item(p, item, NT);
+          const ItemInfo info = load_item<kSplits>(p, item, NT);
           const int b = j & 1;
           if (sparse) {
             ok = mbar_wait(&sm.bm_full[b], (j >> 1) & 1, abort_flag);

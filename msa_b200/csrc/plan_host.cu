@@ -19,9 +19,13 @@ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 inline int tile_rows_of(const msa_plan_desc* d) { return d->tile_rows == 256 ? 256 : kPage; }
 
+inline int kv_splits_of(const msa_plan_desc* d) { return d->dense_kv_splits > 1 ? d->dense_kv_splits : 1; }
+
 int plan_check(const msa_plan_desc* d) {
   if (d == nullptr || d->batch < 0) return MSA_ERR_INVALID;
   if (d->tile_rows != 0 && d->tile_rows != 128 && d->tile_rows != 256) return MSA_ERR_INVALID;
+  if (d->dense_kv_splits < 0 || d->dense_kv_splits > 1024 || (d->dense_kv_splits > 1 && d->tile_rows == 256))
+    return MSA_ERR_INVALID;
   if (d->batch > 0 && (d->qo_lens == nullptr || d->kv_lens == nullptr)) return MSA_ERR_INVALID;
   if (d->num_qo_heads <= 0 || d->num_kv_heads <= 0 || d->num_qo_heads % d->num_kv_heads != 0) return MSA_ERR_INVALID;
   for (int b = 0; b < d->batch; ++b)
@@ -42,11 +46,11 @@ int plan_sizes(const msa_plan_desc* d, int32_t* n_work, int64_t* total_q, int64_
   if (rc != MSA_OK) return rc;
   int64_t nw = 0, tq = 0, tp = 0;
   for (int b = 0; b < d->batch; ++b) {
-    nw += ceil_div(d->qo_lens[b], tile_rows_of(d));
+    nw += ceil_div(d->qo_lens[b], tile_rows_of(d)) * kv_splits_of(d);
     tq += d->qo_lens[b];
     tp += ceil_div(d->kv_lens[b], kPage);
   }
-  if (nw > 0x7fffffffLL || tq > 0x7fffffffLL || tp > 0x7fffffffLL) return MSA_ERR_TOO_LARGE;
+  if (nw > 0x7fffffffLL || tq * kv_splits_of(d) > 0x7fffffffLL || tp > 0x7fffffffLL) return MSA_ERR_TOO_LARGE;
   if (n_work != nullptr) *n_work = static_cast<int32_t>(nw);
   if (total_q != nullptr) *total_q = tq;
   if (total_pages != nullptr) *total_pages = tp;
@@ -82,11 +86,22 @@ int plan(const msa_plan_desc* d, int32_t* work, int32_t* kv_page_indptr, int32_t
       for (int t0 = 0; t0 < ql; t0 += tile) {
         const int rows = std::min(tile, ql - t0);
         const int64_t vis = d->causal ? std::min<int64_t>(kl, static_cast<int64_t>(t0) + rows + off) : kl;
-        Tile t;
-        t.cost = static_cast<int>(std::max<int64_t>(0, ceil_div(vis, kPage)));
-        const int32_t rec[8] = {b, start + t0, rows, t0, kl, off, kv_base, 0};
-        std::memcpy(t.rec, rec, sizeof(rec));
-        tiles.push_back(t);
+        const int n_vis = static_cast<int>(std::max<int64_t>(0, ceil_div(vis, kPage)));
+        const int n_splits = kv_splits_of(d);
+        const int per = static_cast<int>(ceil_div(n_vis, n_splits));
+        for (int s = 0; s < n_splits; ++s) {
+          // split s walks pages [lo, hi) and writes output rows s * total_q + token; a split beyond the visible
+          // pages still gets an entry (lo past the last page: nothing to walk), so that every partial row is written
+          const int lo = std::min(n_vis, s * per), hi = std::min(n_vis, lo + per);
+          if (lo > 0x1fffff) return MSA_ERR_TOO_LARGE;
+          Tile t;
+          t.cost = hi - lo;
+          const int kl_s = (n_splits > 1 && hi > lo) ? std::min<int64_t>(kl, static_cast<int64_t>(hi) * kPage) : kl;
+          const int32_t rec[8] = {b, start + t0, rows | (n_splits > 1 ? lo << 10 : 0), t0, kl_s, off, kv_base,
+                                  static_cast<int32_t>(s * total_q)};
+          std::memcpy(t.rec, rec, sizeof(rec));
+          tiles.push_back(t);
+        }
       }
       start += ql;
       kv_base += d->paged ? static_cast<int>(ceil_div(kl, kPage)) : kl;

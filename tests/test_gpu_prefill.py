@@ -99,6 +99,40 @@ def test_dense_full_mode(qo_lens, kv_lens, Hq, Hkv, kind):
     assert torch.allclose(got[fin], msref[fin], atol=2e-3 if kind == "bf16" else 1e-1, rtol=1e-3)
 
 
+@pytest.mark.parametrize("qo_lens,kv_lens,Hq,Hkv,kind,splits,causal", [
+    ([40, 3], [5000, 9000], 8, 2, "bf16", -1, True),       # planner's own choice (few tiles, long contexts)
+    ([40, 3], [5000, 9000], 8, 2, "fp8", 3, True),
+    ([130], [2100], 2, 1, "bf16", 5, True),                # two tiles; upper splits see nothing of the first rows
+    ([5], [300], 4, 4, "bf16", 7, True),                   # more splits than pages: empty splits
+    ([17], [4000], 6, 2, "fp8", 4, False),
+])
+def test_dense_short_query_kv_splits(qo_lens, kv_lens, Hq, Hkv, kind, splits, causal):
+    """A dense call with few query tiles is split over page ranges and merged (msa_fmha_combine): same output,
+    LSE and max score as the unsplit oracle."""
+    kp, vp, table = make_paged(kv_lens, Hkv, 18)
+    q = torch.randn(sum(qo_lens), Hq, 128, generator=torch.Generator().manual_seed(19)).to(torch.bfloat16)
+    kd, vd, kr, vr, kw = _quantise(kp, vp, kind)
+    plan = msa_b200.fmha_sm100_plan(torch.tensor(qo_lens), torch.tensor(kv_lens), Hq, num_kv_heads=Hkv, page_size=128,
+                                    output_maxscore=True, num_kv_splits=splits, causal=causal)
+    assert plan[3]["dense_kv_splits"] > 1 and not plan[3]["use_decode_kernel"]
+    out, ms, lse = msa_b200.fmha_sm100(q.cuda(), kd, vd, plan, kv_indices=table.cuda(), output_maxscore=True,
+                                       return_lse=True, **kw)
+    assert msa_b200.plan_status(plan) == 0
+    ref, lse_ref = O.dense_attention_paged(q, kr, vr, table, qo_lens, kv_lens, causal=causal)
+    assert (out.float().cpu() - ref).abs().max() <= TOL[kind]
+    assert torch.allclose(lse.cpu(), lse_ref, atol=2e-2, rtol=1e-3)
+    if causal:
+        kraw = kd.float().cpu() if kind == "fp8" else kp
+        msref = O.tile_max_score_paged(q, kraw, table, qo_lens, kv_lens, ms.shape[1])
+        got = ms.cpu()
+        assert torch.equal(torch.isfinite(got), torch.isfinite(msref))
+        fin = torch.isfinite(msref)
+        assert torch.allclose(got[fin], msref[fin], atol=2e-3 if kind == "bf16" else 1e-1, rtol=1e-3)
+    # the same call again reuses the plan's partial buffers
+    out2, _ = msa_b200.fmha_sm100(q.cuda(), kd, vd, plan, kv_indices=table.cuda(), output_maxscore=False, **kw)
+    assert torch.equal(out2, out)
+
+
 def test_score_only_mode_and_reference_fixture():
     z = np.load(os.path.join(G, "maxscore.npz"))
     q = torch.from_numpy(z["q"]).to(torch.bfloat16)

@@ -25,13 +25,13 @@ def test_library_exports_every_declared_symbol():
     lib = msa_b200.get_lib()
     for n in sorted(names):
         assert hasattr(lib, n), f"{n} declared in the header but not exported"
-    assert lib.msa_abi_version() == 2
+    assert lib.msa_abi_version() == 3
     assert lib.msa_error_string(-3).decode().startswith("device-side wait")
 
 
 def test_struct_layout_matches_header_sizes():
     # pointers 8 B, int64 8 B, int32/float 4 B: the ctypes mirror must not be smaller than the C struct
-    assert ctypes.sizeof(_lib.FmhaArgs) % 8 == 0 and ctypes.sizeof(_lib.FmhaArgs) == 208
+    assert ctypes.sizeof(_lib.FmhaArgs) % 8 == 0 and ctypes.sizeof(_lib.FmhaArgs) == 216
     assert ctypes.sizeof(_lib.DecodeArgs) == 144
 
 
@@ -205,6 +205,14 @@ def test_planner_through_the_c_abi():
     assert 2 <= s <= 64
     with pytest.raises(msa_b200.MsaError):
         _host_plan([1], [-5], None, True, True)
+    # KV splits of a dense tile: 3 entries over pages [0,3) [3,6) [6,8), output rows offset by split * total_q,
+    # kv_len cut at the end of each range; a split past the visible pages walks nothing
+    w = _host_plan([5], [1000], None, True, True, 8, 8, dense_kv_splits=3)[0]
+    recs = sorted(w.tolist(), key=lambda r: r[7])
+    assert [(r[2] & 1023, r[2] >> 10, r[4], r[7]) for r in recs] == [(5, 0, 384, 0), (5, 3, 768, 5), (5, 6, 1000, 10)]
+    w = _host_plan([2], [200], None, True, True, 8, 8, dense_kv_splits=4)[0]
+    recs = sorted(w.tolist(), key=lambda r: r[7])
+    assert [(r[2] >> 10, r[4]) for r in recs] == [(0, 128), (1, 200), (2, 200), (2, 200)] and len(recs) == 4
 
 
 def test_c_program_plans_and_validates_through_the_header(tmp_path):
