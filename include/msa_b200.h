@@ -68,8 +68,8 @@ typedef struct msa_plan_desc {
   int32_t kv_block_num;     /* page-list length of a sparse call (> 0), else <= 0 */
   int32_t num_kv_splits;    /* > 0 forces the decode split count, else chosen for whole waves of CTAs */
   int32_t num_sms;          /* SMs the decode split choice may assume (usable_SM_count), <= 0 = 148 */
-  int32_t tile_rows;        /* query rows per work entry: 0 or 128, or 256 for the paired-tile score-only pass
-                               (msa_fmha_args.tile_rows) */
+  int32_t tile_rows;        /* query rows per work entry: 0 or 128 (what msa_fmha_fwd takes); 256 gives 256-row
+                               entries for callers that schedule two tiles at a time themselves */
   int32_t dense_kv_splits;  /* > 1: every query tile becomes this many work entries, each over a contiguous range of
                                the tile's visible pages, writing output rows split * total_q + token (merged by
                                msa_fmha_combine); for dense calls whose query tiles alone cannot fill the GPU.
@@ -177,10 +177,7 @@ typedef struct msa_fmha_args {
   int32_t max_ctas;       /* > 0 caps the persistent grid (the reference's usable_SM_count); 0 = one CTA per SM */
   int32_t qk_dim;         /* 0 or 128: all of the head dimension; 64: the score-only pass (out = NULL) uses only the
                              first 64 elements of q and k (a 64-wide proxy zero-padded to 128 costs half) */
-  int32_t tile_rows;      /* 0 or 128: `work` holds 128-row tiles.  256: `work` holds 256-row tiles (msa_plan_desc.tile_rows
-                             = 256) and each CTA step runs the two 128-row halves side by side against one K page --
-                             only for the score-only pass (out = NULL, no page lists) with an odd number of query
-                             heads per KV head, where there is no second head to pair with (a single proxy head) */
+  int32_t tile_rows;      /* 0 or 128: `work` holds 128-row tiles (the only size the kernels take) */
   const uint8_t* tile_uniform;   /* optional, uint8 [n_work, list_heads] from msa_list_uniformity: non-zero where all
                                     rows of a query tile carry the same page list (the tile's page set is then taken
                                     from one row instead of 128); NULL = no tile is assumed uniform */
@@ -188,6 +185,11 @@ typedef struct msa_fmha_args {
   int64_t max_score_head_stride; /* elements between consecutive heads; 0 = max_k_tiles * tile stride.  The two
                                     strides let a call write its tokens into a slice [.., .., t0:t1] of a larger
                                     score tensor (the decode and prefill halves of a mixed batch) */
+  int32_t k_scale_format;        /* score-only pass over packed e2m1 K (kv_dtype MSA_KV_NVFP4, out = NULL): 0 = one
+                                    e4m3 scale per 16 values (1024 scale bytes per (page, head), two 128x4 tiles),
+                                    1 = one ue8m0 scale per 32 values (MXFP4: 512 bytes, one 128x4 tile; exponents
+                                    outside 2^-24 .. 2^15 saturate) */
+  int32_t reserved0;
   int64_t out_rows;              /* rows of out / lse; 0 = total_q.  dense_kv_splits * total_q when the work list
                                     was planned with KV splits: out and lse are then the partial buffers that
                                     msa_fmha_combine merges (lse must be given) */

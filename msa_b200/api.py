@@ -186,11 +186,6 @@ def _fmha_sm100_plan(
     plan["qo_offset"] = _i32(off, device)
     plan["work"] = torch.from_numpy(work).to(device).contiguous()
     plan["n_work"] = int(work.shape[0])
-    if output_maxscore and not sparse and (num_qo_heads // num_kv_heads) % 2 == 1:
-        # score-only calls over an odd number of heads per KV head (a single proxy head) pair two query tiles
-        # of one head on a CTA instead of two heads: 256-row work entries
-        work2 = _host_plan(qo_lens, kv_lens, off, causal, page_size > 0, num_qo_heads, num_kv_heads, tile_rows=256)[0]
-        plan["work_pair"] = torch.from_numpy(work2).to(device).contiguous()
     plan["dense_kv_splits"] = 1
     if not sparse and total_q > 0 and work.shape[0] > 0:
         # A dense call with few query tiles (a short query over a long context) cannot fill the GPU with one
@@ -316,8 +311,7 @@ def _run_prefill(q, k, v, plan, kv_indices, kv_block_indexes, qo_offset_t, out, 
     a.qk_dim = int(qk_dim)
     a.q, a.k, a.v = _ptr(q), _ptr(k), _ptr(v)
     a.out, a.lse, a.max_score = _ptr(out), _ptr(lse), _ptr(max_score)
-    pair = out is None and kv_block_indexes is None and "work_pair" in plan
-    work = plan["work_pair"] if pair else plan["work"]
+    work = plan["work"]
     n_split = 1
     if (out is not None and kv_block_indexes is None and "work_split" in plan
             and qo_offset_t is plan["qo_offset"]):
@@ -339,7 +333,7 @@ def _run_prefill(q, k, v, plan, kv_indices, kv_block_indexes, qo_offset_t, out, 
     if bool(is_paged) != (plan["page_size"] > 0):
         raise MsaError("the plan and the call disagree on paged vs ragged K/V (pass page_size to fmha_sm100_plan)")
     a.work, a.n_work = _ptr(work), int(work.shape[0])
-    a.tile_rows = 256 if pair else 128
+    a.tile_rows = 128
     a.kv_indices = _ptr(kv_indices)
     a.kv_block_indexes = _ptr(kv_block_indexes)
     a.k_scale_128x4, a.v_scale_128x4 = _ptr(k_sf), _ptr(v_sf)

@@ -3,6 +3,7 @@
 #include <mutex>
 
 #include "fmha_kernel.cuh"
+#include "score_kernel.cuh"
 #include "msa_internal.h"
 
 namespace msa {
@@ -120,10 +121,35 @@ static int launch_fmha_mode(const CUtensorMap& mq, const CUtensorMap& mk, const 
   return static_cast<int>(cudaGetLastError());
 }
 
+// score-only pass: its own kernel, one (query tile, head) per work item
+template <int KVMODE>
+static int launch_score(const CUtensorMap& mq, const CUtensorMap& mk, const FmhaParams& p, int max_ctas,
+                        cudaStream_t st) {
+  using Cfg = ScoreCfg<KVMODE>;
+  static DeviceSetup setup;
+  int num_sms = 0;
+  constexpr int smem = score_smem_bytes<KVMODE>();
+  static_assert(smem <= 232448, "shared memory of the score kernel exceeds the 227 KiB a CTA can have");
+  const int rc = setup.ensure(&num_sms, [] {
+    cudaError_t e = cudaFuncSetAttribute(score_fwd_kernel<KVMODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    // the in-kernel register hand-over only balances if the CTA starts with exactly kRegsLaunch per thread
+    cudaFuncAttributes fa;
+    e = cudaFuncGetAttributes(&fa, score_fwd_kernel<KVMODE>);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (fa.numRegs != Cfg::kRegsLaunch) return static_cast<int>(MSA_ERR_UNSUPPORTED);
+    return static_cast<int>(MSA_OK);
+  });
+  if (rc != MSA_OK) return rc;
+  int ctas = p.n_items < num_sms ? p.n_items : num_sms;
+  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  score_fwd_kernel<KVMODE><<<static_cast<unsigned>(ctas), Cfg::kThreads, smem, st>>>(mq, mk, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
 template <int NT, int KVMODE>
 static int launch_fmha(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
                        const FmhaParams& p, int max_ctas, cudaStream_t st) {
-  if (!p.do_pv) return launch_fmha_mode<NT, KVMODE, true, 0>(mq, mk, mv, mo, p, max_ctas, st);
   return p.sparse ? launch_fmha_mode<NT, KVMODE, false, 1>(mq, mk, mv, mo, p, max_ctas, st)
                   : launch_fmha_mode<NT, KVMODE, false, 0>(mq, mk, mv, mo, p, max_ctas, st);
 }
@@ -149,6 +175,11 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
   if (a->qk_dim != 0 && a->qk_dim != 64 && a->qk_dim != 128) return MSA_ERR_INVALID;
   if (a->qk_dim == 64 && (a->out != nullptr || a->kv_dtype == MSA_KV_NVFP4)) return MSA_ERR_UNSUPPORTED;
   if (a->out_rows != 0 && (a->out_rows < a->total_q || a->out == nullptr || a->lse == nullptr)) return MSA_ERR_INVALID;
+  const bool score_only = a->out == nullptr;
+  if (score_only && sparse) return MSA_ERR_UNSUPPORTED;        // the pass over page lists has no max-score output
+  if (a->k_scale_format != 0 && (a->k_scale_format != 1 || !score_only || a->kv_dtype != MSA_KV_NVFP4))
+    return MSA_ERR_INVALID;
+  if (a->tile_rows != 0 && a->tile_rows != 128) return MSA_ERR_INVALID;
   if (a->n_work <= 0 || a->total_q <= 0) return MSA_OK;
   const int64_t out_rows = a->out_rows > 0 ? a->out_rows : a->total_q;
 
@@ -164,6 +195,8 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
   p.tile_uniform = sparse ? a->tile_uniform : nullptr;
   p.k_scale_bytes = a->k_scale_128x4;
   p.v_scale_bytes = a->v_scale_128x4;
+  p.k_scale_tile_bytes = a->k_scale_format == 1 ? 512 : 1024;
+  p.k_mx = a->k_scale_format == 1;
   p.k_raw = static_cast<const uint8_t*>(a->k);
   p.v_raw = static_cast<const uint8_t*>(a->v);
   p.Hq = a->num_qo_heads;
@@ -187,17 +220,9 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
 
   // two query heads share one K/V stream when they share a KV head and a page list
   int nt = (p.hr % 2 == 0 && (!sparse || a->list_heads == a->num_kv_heads)) ? 2 : 1;
+  if (score_only) nt = 1;   // the score kernel takes one head per work item
   p.pair_tiles = 0;
   p.n_head_groups = p.Hq / nt;
-  if (a->tile_rows == 256) {
-    // no second head to pair with: the two tiles of a CTA are the halves of a 256-row work entry of one head
-    if (nt != 1 || sparse || a->out != nullptr) return MSA_ERR_UNSUPPORTED;
-    nt = 2;
-    p.pair_tiles = 1;
-    p.n_head_groups = p.Hq;
-  } else if (a->tile_rows != 0 && a->tile_rows != 128) {
-    return MSA_ERR_INVALID;
-  }
   const long long n_items = static_cast<long long>(p.n_work) * p.n_head_groups;
   if (n_items > 0x7fffffffLL) return MSA_ERR_TOO_LARGE;
   p.n_items = static_cast<int>(n_items);
@@ -217,6 +242,14 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
     if (rc != MSA_OK) return rc;
     rc = make_kv_map(&mv, a->v != nullptr ? a->v : a->k, a->kv_rows, p.Hkv, a->paged, fp8, 0);
     if (rc != MSA_OK) return rc;
+  }
+  if (score_only) {
+    switch (a->kv_dtype) {
+      case MSA_KV_BF16: return launch_score<KV_BF16>(mq, mk, p, a->max_ctas, st);
+      case MSA_KV_FP8_E4M3: return launch_score<KV_FP8>(mq, mk, p, a->max_ctas, st);
+      case MSA_KV_NVFP4: return launch_score<KV_NVFP4>(mq, mk, p, a->max_ctas, st);
+    }
+    return MSA_ERR_UNSUPPORTED;
   }
   switch (a->kv_dtype * 2 + (nt - 1)) {
     case 0: return launch_fmha<1, KV_BF16>(mq, mk, mv, mo, p, a->max_ctas, st);

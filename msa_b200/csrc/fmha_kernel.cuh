@@ -74,6 +74,9 @@ struct FmhaParams {
   const uint8_t* tile_uniform;   // [n_work, list_heads]: 1 = every row of the query tile has the same list; or null
   const uint8_t* k_scale_bytes;  // NVFP4: e4m3 block scales in 128x4 tiles, one 1 KiB block per (page, head)
   const uint8_t* v_scale_bytes;
+  int k_scale_tile_bytes;        // score-only pass over packed e2m1 K: scale bytes per (page, head): 1024 (e4m3 per 16
+                                 // values) or 512 (ue8m0 per 32 values, k_mx)
+  int k_mx;
   const uint8_t* k_raw;          // NVFP4 raw page storage
   const uint8_t* v_raw;
   int Hq, Hkv, hr, topk, list_heads, total_q, max_k_tiles, n_work, n_head_groups, n_items;

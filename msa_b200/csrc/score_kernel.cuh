@@ -1,0 +1,571 @@
+// Score-only pass on sm_100a: per-page maxima of Q K^T (stage 1 of the sparse pipeline, the "proxy" pass), the
+// mode OnlyScore of the reference's FMHA kernel
+// (csrc/include/sm100_fmha_fwd_mainloop_tma_warpspecialized.hpp:842-1109, reached from
+// fmha_sm100(..., output_o=False, output_maxscore=True), python/fmha_sm100/api.py:1028).
+//
+// A kernel of its own because nothing of the attention kernel's structure fits it: there is no P, no V and no O, so
+// the only work besides the MMAs is one row maximum per (query row, page), and what bounds the loop is the
+// hand-over between the single MMA-issuing thread and the warps that read S.  Layout of one persistent CTA
+// (384 threads, one per SM, items = (128-row query tile, query head), heaviest first):
+//
+//   warp 8     producer: Q of the next item into the other Q buffer, K pages two at a time into a ring of
+//              page PAIRS (the two pages of a pair lie back to back, so they form one 256-row operand)
+//   warp 9     MMA issuer: one tcgen05.mma per k-step with N = 256 covers both pages of a pair (half as many
+//              instructions, commits and barrier polls per page as N = 128); S pairs alternate between TMEM
+//              columns [0, 256) and [256, 512); tcgen05.commit releases the K pair and, after an item's last
+//              pair, the Q buffer
+//   warps 0-3  row-max warpgroup 0: thread = query row; reads the first page's 128 S columns of every pair,
+//   warps 4-7  row-max warpgroup 1: the second page's.  Both groups work on the SAME 128 query rows, so a pair of
+//              pages costs each of them one page of work while the tensor pipe needs two pages of time.
+//   warps 10-11 (NVFP4 / MXFP4 K only) dequantise raw pages into f16 operand tiles
+//
+// K formats: bf16 (TMA, 128-byte swizzle), e4m3 fed to kind::f8f6f4 as stored against a two-term e4m3 Q
+// (q = s (hi + lo), s a power of two per row), packed e2m1 with e4m3 (group 16) or ue8m0 (group 32) block scales
+// dequantised exactly into f16.
+#pragma once
+
+#include "fmha_kernel.cuh"
+
+namespace msa {
+
+template <int KVMODE>
+struct ScoreCfg {
+  static constexpr bool kQuant = KVMODE != KV_BF16;
+  static constexpr bool kKDirectFp8 = KVMODE == KV_FP8;
+  static constexpr bool kKConvert = KVMODE == KV_NVFP4;
+  static constexpr int kPageBytes = kKDirectFp8 ? kHalfBytes : kTileBytes;   // one page as an MMA operand
+  static constexpr int kPairBytes = 2 * kPageBytes;
+  static constexpr int kPairs = kKDirectFp8 ? 4 : 2;                         // ring depth: 128 KiB of K
+  static constexpr int kRawStages = kKConvert ? 3 : 0;
+  static constexpr int kRawBytes = 8192 + 1024;                              // packed e2m1 page + its scales
+  static constexpr int kThreads = 384;
+  static constexpr int kProducerWarp = 8, kMmaWarp = 9, kCvtWarp0 = 10;
+  // 256 row-max threads at 216 registers + 128 helper threads at 72 = 384 x 168 (see FmhaCfg)
+  static constexpr int kRegsLaunch = 168, kRegsRowMax = 216, kRegsHelper = 72;
+  static_assert(256 * kRegsRowMax + 128 * kRegsHelper == 384 * kRegsLaunch, "setmaxnreg budget must balance");
+  static constexpr int kFmt16 = kQuant ? 0 : 1;   // f16 once K is dequantised, bf16 as loaded
+};
+
+template <int KVMODE>
+struct __align__(1024) ScoreSmem {
+  using Cfg = ScoreCfg<KVMODE>;
+  uint8_t q[2][kTileBytes];
+  uint8_t k[Cfg::kPairs][Cfg::kPairBytes];
+  uint8_t raw[Cfg::kRawStages > 0 ? Cfg::kRawStages : 1][Cfg::kRawStages > 0 ? Cfg::kRawBytes : 16];
+  float q_row_scale[2][128];   // e4m3 K: power-of-two scale of every rewritten Q row
+  uint64_t q_full[2], q_ready[2], q_empty[2];
+  uint64_t k_full[Cfg::kPairs], k_empty[Cfg::kPairs];
+  uint64_t raw_full[Cfg::kRawStages > 0 ? Cfg::kRawStages : 1], raw_empty[Cfg::kRawStages > 0 ? Cfg::kRawStages : 1];
+  uint64_t sc_full[2], sc_free[2];
+  uint32_t tmem_base;
+  int abort;
+};
+
+template <int KVMODE>
+constexpr int score_smem_bytes() {
+  return static_cast<int>(sizeof(ScoreSmem<KVMODE>)) + 1024;
+}
+
+// One query tile x one head.
+struct ScoreItem {
+  int tok0, rows, qloc0, h, g, kv_len, qo_off, kv_base, n_pages;
+};
+
+__device__ __forceinline__ ScoreItem score_item(const FmhaParams& p, int item) {
+  ScoreItem it;
+  const int wi = item / p.Hq;
+  it.h = item - wi * p.Hq;   // head fastest: CTAs running side by side share K pages
+  it.g = it.h / p.hr;
+  const int4 w = __ldg(p.work + 2 * wi), w2 = __ldg(p.work + 2 * wi + 1);
+  it.tok0 = w.y;
+  it.rows = w.z;
+  it.qloc0 = w.w;
+  it.kv_len = w2.x;
+  it.qo_off = w2.y;
+  it.kv_base = w2.z;
+  int vis = it.kv_len;   // keys visible to the last row of the tile
+  if (p.causal) vis = min(vis, it.qloc0 + it.rows + it.qo_off);
+  it.n_pages = vis > 0 ? (vis + 127) >> 7 : 0;
+  return it;
+}
+
+// S[:, d .. d + N) = Q K^T for one pair (N = 256) or one page (N = 128)
+template <class Cfg, int N>
+__device__ __forceinline__ void issue_score_qk(uint32_t q_saddr, uint32_t k_saddr, uint32_t d, bool half_dim) {
+  constexpr uint32_t desc_hi = smem_desc_hi(1024);
+  const uint32_t qa = smem_desc_lo(q_saddr, 16), ka = smem_desc_lo(k_saddr, 16);
+  if constexpr (Cfg::kKDirectFp8) {
+    // Q_hi on the first 16 KiB of the Q tile, Q_lo on the second; 32 contraction bytes per step
+    constexpr uint32_t idesc = make_idesc(128, N, 0, 0, 0, 0);
+    umma_ss_lohi<0, 1>(d, qa, ka, desc_hi, idesc);
+    umma_ss_lohi<1, 1>(d, qa + 2, ka + 2, desc_hi, idesc);
+    if (!half_dim) {
+      umma_ss_lohi<1, 1>(d, qa + 4, ka + 4, desc_hi, idesc);
+      umma_ss_lohi<1, 1>(d, qa + 6, ka + 6, desc_hi, idesc);
+    }
+    umma_ss_lohi<1, 1>(d, qa + 1024, ka, desc_hi, idesc);
+    umma_ss_lohi<1, 1>(d, qa + 1026, ka + 2, desc_hi, idesc);
+    if (!half_dim) {
+      umma_ss_lohi<1, 1>(d, qa + 1028, ka + 4, desc_hi, idesc);
+      umma_ss_lohi<1, 1>(d, qa + 1030, ka + 6, desc_hi, idesc);
+    }
+  } else {
+    // 16-bit operands: the 64-element halves of Q are 16 KiB apart, those of a K pair 32 KiB (descriptor units
+    // of 16 bytes: 1024 and 2048)
+    constexpr uint32_t idesc = make_idesc(128, N, Cfg::kFmt16, Cfg::kFmt16, 0, 0);
+    umma_ss_lohi<0, 0>(d, qa, ka, desc_hi, idesc);
+    umma_ss_lohi<1, 0>(d, qa + 2, ka + 2, desc_hi, idesc);
+    umma_ss_lohi<1, 0>(d, qa + 4, ka + 4, desc_hi, idesc);
+    umma_ss_lohi<1, 0>(d, qa + 6, ka + 6, desc_hi, idesc);
+    if (!half_dim) {
+      umma_ss_lohi<1, 0>(d, qa + 1024, ka + 2048, desc_hi, idesc);
+      umma_ss_lohi<1, 0>(d, qa + 1026, ka + 2050, desc_hi, idesc);
+      umma_ss_lohi<1, 0>(d, qa + 1028, ka + 2052, desc_hi, idesc);
+      umma_ss_lohi<1, 0>(d, qa + 1030, ka + 2054, desc_hi, idesc);
+    }
+  }
+}
+
+template <int KVMODE>
+__global__ void __launch_bounds__(384, 1)
+score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                 const FmhaParams p) {
+  using Cfg = ScoreCfg<KVMODE>;
+  using Smem = ScoreSmem<KVMODE>;
+  constexpr int NP = Cfg::kPairs;
+  constexpr int NRAW = Cfg::kRawStages > 0 ? Cfg::kRawStages : 1;
+  extern __shared__ uint8_t smem_raw[];
+  Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  volatile int* abort_flag = &sm.abort;
+  MSA_TDECL
+
+  if (tid == 0) {
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sm.q_full[b], 1);
+      mbar_init(&sm.q_ready[b], 8);     // one arrival per row-max warp
+      mbar_init(&sm.q_empty[b], 1);
+      mbar_init(&sm.sc_full[b], 1);
+      mbar_init(&sm.sc_free[b], 8);
+    }
+    for (int s = 0; s < NP; ++s) {
+      mbar_init(&sm.k_full[s], Cfg::kKConvert ? 2 : 1);
+      mbar_init(&sm.k_empty[s], 1);
+    }
+    for (int s = 0; s < NRAW; ++s) {
+      mbar_init(&sm.raw_full[s], 1);
+      mbar_init(&sm.raw_empty[s], 2);
+    }
+    sm.abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == Cfg::kMmaWarp) {
+    tmem_alloc(&sm.tmem_base, 512);
+    tmem_relinquish();
+  }
+  if (warp == Cfg::kProducerWarp && lane == 0) {
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+
+  // The j-th item of this CTA that has pages to visit (the list is heaviest first; rounds alternate direction so
+  // that the CTA with the heaviest item of one round takes the lightest of the next), or -1 past the end.
+  auto item_of = [&](int j) {
+    const int base = j * static_cast<int>(gridDim.x);
+    const int idx = (j & 1) ? base + static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)
+                            : base + static_cast<int>(blockIdx.x);
+    return (base < p.n_items && idx < p.n_items) ? idx : -1;
+  };
+  // every role walks the same sequence: items without a visible page are skipped by all of them
+  auto next_item = [&](int& j, ScoreItem& it) -> bool {
+    for (;; ++j) {
+      const int item = item_of(j);
+      if (item < 0) {
+        if (j * static_cast<int>(gridDim.x) >= p.n_items) return false;
+        continue;   // a hole in the last (partial) round
+      }
+      it = score_item(p, item);
+      if (it.n_pages > 0) return true;
+    }
+  };
+
+  if (warp < 8) {
+    // =========================================================================
+    // row-max warpgroup w: the w-th page of every pair
+    // =========================================================================
+    setmaxnreg_inc<Cfg::kRegsRowMax>();
+    const int w = warp >> 2;
+    const int r = tid & 127;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    bool ok = true;
+    uint32_t pair_seq = 0, n_q = 0;
+
+    // Q of item number n_q (buffer n_q & 1) into the operand format of the quantised modes.  Rows 0-63 are
+    // rewritten by warps 0-1 of group 0, rows 64-127 by warps 2-3 of group 1; every warp arrives.
+    auto convert_q = [&](uint32_t nq) {
+      if constexpr (Cfg::kQuant) {
+        const int qb = nq & 1;
+        ok = ok && mbar_wait(&sm.q_full[qb], (nq >> 1) & 1, abort_flag);
+        if (ok) {
+          if constexpr (Cfg::kKDirectFp8) {
+            if ((r >> 6) == w) {
+              // my row -> two e4m3 rows (hi, lo) sharing one power-of-two scale; hi lands on the first
+              // 64-column half of the bf16 tile, lo on the second, same row: in place, thread-private
+              uint8_t* rowp = sm.q[qb] + r * 128;
+              uint4 x[16];
+#pragma unroll
+              for (int c = 0; c < 16; ++c)
+                x[c] = *reinterpret_cast<const uint4*>(rowp + (c >> 3) * kHalfBytes + (((c & 7) ^ (r & 7)) << 4));
+              float amax = 0.f;
+#pragma unroll
+              for (int c = 0; c < 16; ++c) {
+                const uint32_t v[4] = {x[c].x, x[c].y, x[c].z, x[c].w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  amax = fmaxf(amax, fabsf(__uint_as_float(v[i] << 16)));
+                  amax = fmaxf(amax, fabsf(__uint_as_float(v[i] & 0xffff0000u)));
+                }
+              }
+              float sq = 1.0f;   // power of two that brings the row maximum into [224, 448]
+              if (amax > 0.f && amax < 3.0e38f) {
+                int e;
+                frexpf(amax, &e);
+                sq = ldexpf(1.0f, e - 9);
+                if (amax / sq > 448.0f) sq *= 2.0f;
+              }
+              const float inv = 1.0f / sq;
+              sm.q_row_scale[qb][r] = sq;
+#pragma unroll
+              for (int c8 = 0; c8 < 8; ++c8) {
+                uint32_t hi4[4], lo4[4];
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                  const uint4 xv = x[c8 * 2 + half];
+                  const uint32_t v[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+                  for (int i = 0; i < 4; i += 2) {
+                    float y[4] = {__uint_as_float(v[i] << 16) * inv, __uint_as_float(v[i] & 0xffff0000u) * inv,
+                                  __uint_as_float(v[i + 1] << 16) * inv, __uint_as_float(v[i + 1] & 0xffff0000u) * inv};
+                    const uint32_t h01 = f32x2_to_e4m3x2(y[0], y[1]), h23 = f32x2_to_e4m3x2(y[2], y[3]);
+                    float f[4];
+                    e4m3x2_to_f32x2(h01, f[0], f[1]);
+                    e4m3x2_to_f32x2(h23, f[2], f[3]);
+                    const uint32_t l01 = f32x2_to_e4m3x2(y[0] - f[0], y[1] - f[1]);
+                    const uint32_t l23 = f32x2_to_e4m3x2(y[2] - f[2], y[3] - f[3]);
+                    hi4[half * 2 + (i >> 1)] = h01 | (h23 << 16);
+                    lo4[half * 2 + (i >> 1)] = l01 | (l23 << 16);
+                  }
+                }
+                const uint32_t off = ((c8 ^ (r & 7)) << 4);
+                *reinterpret_cast<uint4*>(rowp + off) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
+                *reinterpret_cast<uint4*>(rowp + kHalfBytes + off) = make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]);
+              }
+            }
+          } else {
+            // bf16 -> f16 in place (the dequantised K tiles are f16 and the tensor core wants one format)
+            uint4* qv = reinterpret_cast<uint4*>(sm.q[qb]);
+            for (int i = w * 128 + r; i < kTileBytes / 16; i += 256) {
+              uint4 xq = qv[i];
+              xq.x = bf16x2_to_f16x2(xq.x);
+              xq.y = bf16x2_to_f16x2(xq.y);
+              xq.z = bf16x2_to_f16x2(xq.z);
+              xq.w = bf16x2_to_f16x2(xq.w);
+              qv[i] = xq;
+            }
+          }
+          fence_proxy_async();
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.q_ready[qb]);
+      }
+    };
+
+    int j = 0, j_next = 0;
+    ScoreItem it, it_next;
+    bool have = next_item(j, it);
+    if (have) convert_q(0);
+    while (have && ok) {
+      j_next = j + 1;
+      const bool have_next = next_item(j_next, it_next);
+      const bool row_valid = r < it.rows;
+      int limit_base = -1;
+      if (row_valid) {
+        limit_base = it.kv_len - 1;
+        if (p.causal) limit_base = min(limit_base, it.qloc0 + r + it.qo_off);
+      }
+      float row_scale = 1.0f;
+      float* dst = p.max_score + static_cast<long long>(it.h) * p.ms_head + it.tok0 + r;
+      const int n = it.n_pages, n_pairs = (n + 1) >> 1;
+      for (int pi = 0; pi < n_pairs && ok; ++pi, ++pair_seq) {
+        const int sb = pair_seq & 1;
+        MSA_TBEGIN
+        ok = mbar_wait(&sm.sc_full[sb], (pair_seq >> 1) & 1, abort_flag);
+        MSA_TEND(0)
+        if (!ok) break;
+        tc_fence_after();
+        if (r == 0) { MSA_TRACE(w * 2, pair_seq, clock64()) }
+        MSA_TBEGIN
+        const int page = n - 1 - (2 * pi + w);   // pages are walked from the highest down
+        if (page >= 0) {
+          if constexpr (Cfg::kKDirectFp8) {
+            if (pi == 0) row_scale = sm.q_row_scale[n_q & 1][r];
+          }
+          uint32_t sr[128];
+          const uint32_t s_cur = tmem + lane_base + sb * 256 + w * 128;
+          tmem_ld32p(s_cur, sr);
+          tmem_ld32p(s_cur + 32, sr + 32);
+          tmem_ld32p(s_cur + 64, sr + 64);
+          tmem_ld32p(s_cur + 96, sr + 96);
+          tmem_ld_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sm.sc_free[sb]);   // S is in registers: the MMA warp may overwrite it
+          const int limit = limit_base - (page << 7);
+          if (!__all_sync(0xffffffffu, limit >= 127)) {
+#pragma unroll
+            for (int c = 0; c < 128; ++c) sr[c] = (c <= limit) ? sr[c] : 0xff800000u;
+          }
+          float t0 = -INFINITY, t1 = -INFINITY, t2 = -INFINITY, t3 = -INFINITY;
+#pragma unroll
+          for (int c = 0; c < 128; c += 8) {
+            t0 = max3(t0, __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
+            t1 = max3(t1, __uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3]));
+            t2 = max3(t2, __uint_as_float(sr[c + 4]), __uint_as_float(sr[c + 5]));
+            t3 = max3(t3, __uint_as_float(sr[c + 6]), __uint_as_float(sr[c + 7]));
+          }
+          const float tmax = fmaxf(fmaxf(t0, t1), fmaxf(t2, t3));
+          if (row_valid) __stwt(dst + static_cast<long long>(page) * p.ms_tile, tmax * row_scale);
+        } else {
+          // the last pair of an odd walk has no second page: nothing to read, but the buffer still takes my arrival
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sm.sc_free[sb]);
+        }
+        MSA_TEND(1)
+        // Q of the next item is rewritten while the MMA warp still has this item's pairs in hand.  The producer
+        // issues that Q load right after K pair min(1, n_pairs - 1) of this item (see there), so waiting for it at
+        // the same pair cannot dead-lock: the ring holds at least two pairs.
+        if (pi == min(1, n_pairs - 1) && have_next) convert_q(n_q + 1);
+      }
+      ++n_q;
+      have = have_next;
+      it = it_next;
+      j = j_next;
+    }
+    MSA_TFLUSH(r == 0 && w == 0, 0, 3)
+  } else {
+    setmaxnreg_dec<Cfg::kRegsHelper>();
+    if (warp == Cfg::kProducerWarp) {
+      // =======================================================================
+      // producer: Q per item, K per pair (lane 0)
+      // =======================================================================
+      if (lane == 0) {
+        bool ok = true;
+        uint32_t n_q = 0, pair_seq = 0, raw_seq = 0;
+        // Q of the item numbered n_q into buffer n_q & 1, once the item that used the buffer two items ago is done
+        auto load_q = [&](const ScoreItem& qi) {
+          const int qb = n_q & 1;
+          MSA_TBEGIN
+          ok = mbar_wait(&sm.q_empty[qb], ((n_q >> 1) & 1) ^ 1, abort_flag);
+          MSA_TEND(12)
+          if (!ok) return;
+          ++n_q;
+          mbar_expect_tx(&sm.q_full[qb], kTileBytes);
+          tma_load_3d(sm.q[qb], &tmap_q, &sm.q_full[qb], 0, qi.h, qi.tok0);
+          tma_load_3d(sm.q[qb] + kHalfBytes, &tmap_q, &sm.q_full[qb], 64, qi.h, qi.tok0);
+        };
+        int j = 0, j_next = 0;
+        ScoreItem it, it_next;
+        bool have = next_item(j, it);
+        if (have) load_q(it);
+        while (have && ok) {
+          j_next = j + 1;
+          const bool have_next = next_item(j_next, it_next);
+          const int n = it.n_pages, n_pairs = (n + 1) >> 1;
+          const int page_base = p.paged ? it.kv_base : 0;
+          const int tok_base = p.paged ? 0 : it.kv_base;
+          for (int pi = 0; pi < n_pairs && ok; ++pi, ++pair_seq) {
+            const int np = min(2, n - 2 * pi);
+            const int kq = pair_seq % NP;
+            if constexpr (Cfg::kKConvert) {
+              for (int e = 0; e < np && ok; ++e, ++raw_seq) {
+                const int page = n - 1 - (2 * pi + e);
+                const int phys = __ldg(p.kv_indices + page_base + page);
+                const size_t tile = static_cast<size_t>(phys) * p.Hkv + it.g;
+                const int s = raw_seq % NRAW;
+                MSA_TBEGIN
+                ok = mbar_wait(&sm.raw_empty[s], ((raw_seq / NRAW) & 1) ^ 1, abort_flag);
+                MSA_TEND(13)
+                if (!ok) break;
+                mbar_expect_tx(&sm.raw_full[s], 8192 + p.k_scale_tile_bytes);
+                bulk_load(sm.raw[s], p.k_raw + tile * 8192, 8192, &sm.raw_full[s]);
+                bulk_load(sm.raw[s] + 8192, p.k_scale_bytes + tile * p.k_scale_tile_bytes, p.k_scale_tile_bytes,
+                          &sm.raw_full[s]);
+              }
+            } else {
+              MSA_TBEGIN
+              ok = mbar_wait(&sm.k_empty[kq], ((pair_seq / NP) & 1) ^ 1, abort_flag);
+              MSA_TEND(13)
+              if (!ok) break;
+              mbar_expect_tx(&sm.k_full[kq], np * Cfg::kPageBytes);
+              for (int e = 0; e < np; ++e) {
+                const int page = n - 1 - (2 * pi + e);
+                const int phys = p.paged ? __ldg(p.kv_indices + page_base + page) : 0;
+                const int tok_k = tok_base + (page << 7);
+                uint8_t* kdst = sm.k[kq] + e * kHalfBytes;   // second page: rows 128-255 of the operand
+                if constexpr (Cfg::kKDirectFp8) {
+                  if (p.paged)
+                    tma_load_4d(kdst, &tmap_k, &sm.k_full[kq], 0, 0, it.g, phys);
+                  else
+                    tma_load_3d(kdst, &tmap_k, &sm.k_full[kq], 0, it.g, tok_k);
+                } else if (p.paged) {
+                  tma_load_4d(kdst, &tmap_k, &sm.k_full[kq], 0, 0, it.g, phys);
+                  tma_load_4d(kdst + kTileBytes, &tmap_k, &sm.k_full[kq], 64, 0, it.g, phys);
+                } else {
+                  tma_load_3d(kdst, &tmap_k, &sm.k_full[kq], 0, it.g, tok_k);
+                  tma_load_3d(kdst + kTileBytes, &tmap_k, &sm.k_full[kq], 64, it.g, tok_k);
+                }
+              }
+            }
+            // the next item's Q goes out early, so that the row-max warps can rewrite it inside this item
+            if (ok && pi == min(1, n_pairs - 1) && have_next) load_q(it_next);
+          }
+          have = have_next;
+          it = it_next;
+          j = j_next;
+        }
+        MSA_TFLUSH(true, 12, 14)
+      }
+    } else if (warp == Cfg::kMmaWarp) {
+      // =======================================================================
+      // MMA issuer
+      // =======================================================================
+      bool ok = true;
+      uint32_t n_q = 0, pair_seq = 0;
+      int j = 0;
+      ScoreItem it;
+      while (ok && next_item(j, it)) {
+        const int qb = n_q & 1;
+        MSA_TBEGIN
+        ok = mbar_wait(Cfg::kQuant ? &sm.q_ready[qb] : &sm.q_full[qb], (n_q >> 1) & 1, abort_flag);
+        MSA_TEND(14)
+        if (!ok) break;
+        ++n_q;
+        const uint32_t qaddr = smem_u32(sm.q[qb]);
+        const int n = it.n_pages, n_pairs = (n + 1) >> 1;
+        for (int pi = 0; pi < n_pairs && ok; ++pi, ++pair_seq) {
+          const int np = min(2, n - 2 * pi);
+          const int kq = pair_seq % NP, sb = pair_seq & 1;
+          MSA_TBEGIN
+          ok = mbar_wait(&sm.k_full[kq], (pair_seq / NP) & 1, abort_flag);
+          MSA_TEND(6)
+          MSA_TBEGIN
+          if (ok && pair_seq >= 2) ok = mbar_wait(&sm.sc_free[sb], ((pair_seq >> 1) + 1) & 1, abort_flag);
+          MSA_TEND(4)
+          if (!ok) break;
+          tc_fence_after();
+          MSA_TBEGIN
+          if (lane == 0) {
+            const uint32_t kaddr = smem_u32(sm.k[kq]);
+            if (np == 2) issue_score_qk<Cfg, 256>(qaddr, kaddr, sb * 256, p.half_dim != 0);
+            else issue_score_qk<Cfg, 128>(qaddr, kaddr, sb * 256, p.half_dim != 0);
+            umma_commit(&sm.sc_full[sb]);
+            umma_commit(&sm.k_empty[kq]);                       // the pair is free once these MMAs have read it
+            if (pi + 1 == n_pairs) umma_commit(&sm.q_empty[qb]);  // and Q after the item's last pair
+          }
+          __syncwarp();
+          MSA_TEND(5)
+        }
+        ++j;
+      }
+      MSA_TFLUSH(lane == 0, 4, 7)
+      MSA_TFLUSH(lane == 0, 14, 15)
+    } else if constexpr (Cfg::kKConvert) {
+      // =======================================================================
+      // dequantise raw e2m1 pages into f16 operand tiles (64 threads; a thread owns one 16-value block of every
+      // 8th row).  Block scales: e4m3 per 16 values (two 128x4 tiles per page) or, with k_mx, ue8m0 per 32 (one).
+      // =======================================================================
+      const int ct = tid - Cfg::kCvtWarp0 * 32;  // 0..63
+      const int r8 = ct >> 3, c8 = ct & 7;
+      const uint32_t sw0 = (((c8 & 3) * 2) ^ r8) << 4, sw1 = (((c8 & 3) * 2 + 1) ^ r8) << 4;
+      const bool mx = p.k_mx != 0;
+      bool ok = true;
+      uint32_t raw_seq = 0, pair_seq = 0;
+      int j = 0;
+      ScoreItem it;
+      while (ok && next_item(j, it)) {
+        const int n = it.n_pages, n_pairs = (n + 1) >> 1;
+        for (int pi = 0; pi < n_pairs && ok; ++pi, ++pair_seq) {
+          const int np = min(2, n - 2 * pi);
+          const int kq = pair_seq % NP;
+          ok = mbar_wait(&sm.k_empty[kq], ((pair_seq / NP) & 1) ^ 1, abort_flag);
+          for (int e = 0; e < np && ok; ++e, ++raw_seq) {
+            const int rs = raw_seq % NRAW;
+            ok = mbar_wait(&sm.raw_full[rs], (raw_seq / NRAW) & 1, abort_flag);
+            if (!ok) break;
+            const uint8_t* rawp = sm.raw[rs];
+            uint8_t* dst = sm.k[kq] + e * kHalfBytes + (c8 >> 2) * kTileBytes + r8 * 128;
+            const uint8_t* src = rawp + ct * 8;
+            // scale of (row, block): 128x4 tile offset (row % 32) * 16 + (row / 32) * 4 + block % 4; with ue8m0
+            // scales a block of 16 values shares the scale of its group of 32 (block c8 -> group c8 / 2)
+            const uint8_t* sc = mx ? rawp + 8192 + r8 * 16 + (c8 >> 1) : rawp + 8192 + (c8 >> 2) * 512 + r8 * 16 + (c8 & 3);
+#pragma unroll 4
+            for (int i = 0; i < 16; ++i) {
+              const uint2 x = *reinterpret_cast<const uint2*>(src + i * 512);
+              const uint32_t sb = sc[(i & 3) * 128 + (i >> 2) * 4];
+              uint32_t s2;
+              if (mx) {
+                // 2^(e - 127) as f16, exact for exponents -24 .. 15 (clamped outside)
+                const int ex = min(max(static_cast<int>(sb) - 127, -24), 15);
+                const uint32_t h = ex >= -14 ? static_cast<uint32_t>(ex + 15) << 10 : 1u << (ex + 24);
+                s2 = h | (h << 16);
+              } else {
+                uint32_t s2hi;
+                cvt_e4m3x4_f16x4(sb | (sb << 8), s2, s2hi);
+              }
+              uint32_t f0[4], f1[4];
+              cvt_e2m1x8_f16x8(x.x, f0);
+              cvt_e2m1x8_f16x8(x.y, f1);
+              uint4 a, b;
+              a.x = hmul2_u32(f0[0], s2);
+              a.y = hmul2_u32(f0[1], s2);
+              a.z = hmul2_u32(f0[2], s2);
+              a.w = hmul2_u32(f0[3], s2);
+              b.x = hmul2_u32(f1[0], s2);
+              b.y = hmul2_u32(f1[1], s2);
+              b.z = hmul2_u32(f1[2], s2);
+              b.w = hmul2_u32(f1[3], s2);
+              *reinterpret_cast<uint4*>(dst + i * 1024 + sw0) = a;
+              *reinterpret_cast<uint4*>(dst + i * 1024 + sw1) = b;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.raw_empty[rs]);
+          }
+          if (!ok) break;
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sm.k_full[kq]);
+        }
+        ++j;
+      }
+    }
+  }
+
+  // ---- teardown ---------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == Cfg::kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+  if (tid == 0 && sm.abort) atomicExch(p.status, MSA_ERR_TIMEOUT);
+}
+
+}  // namespace msa
