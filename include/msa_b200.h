@@ -68,8 +68,8 @@ typedef struct msa_plan_desc {
   int32_t kv_block_num;     /* page-list length of a sparse call (> 0), else <= 0 */
   int32_t num_kv_splits;    /* > 0 forces the decode split count, else chosen for whole waves of CTAs */
   int32_t num_sms;          /* SMs the decode split choice may assume (usable_SM_count), <= 0 = 148 */
-  int32_t tile_rows;        /* query rows per work entry: 0 or 128 (what msa_fmha_fwd takes); 256 gives 256-row
-                               entries for callers that schedule two tiles at a time themselves */
+  int32_t tile_rows;        /* query rows per work entry: 0 or 128; 256 for the score-only pass, whose work items
+                               are two query tiles against one stream of K pages (msa_fmha_args.tile_rows) */
   int32_t dense_kv_splits;  /* > 1: every query tile becomes this many work entries, each over a contiguous range of
                                the tile's visible pages, writing output rows split * total_q + token (merged by
                                msa_fmha_combine); for dense calls whose query tiles alone cannot fill the GPU.
@@ -177,7 +177,10 @@ typedef struct msa_fmha_args {
   int32_t max_ctas;       /* > 0 caps the persistent grid (the reference's usable_SM_count); 0 = one CTA per SM */
   int32_t qk_dim;         /* 0 or 128: all of the head dimension; 64: the score-only pass (out = NULL) uses only the
                              first 64 elements of q and k (a 64-wide proxy zero-padded to 128 costs half) */
-  int32_t tile_rows;      /* 0 or 128: `work` holds 128-row tiles (the only size the kernels take) */
+  int32_t tile_rows;      /* 0 or 128: `work` holds 128-row tiles.  256 (score-only pass, out = NULL, only): `work`
+                             holds 256-row entries (msa_plan_desc.tile_rows = 256), so that every K page is fetched
+                             once for two query tiles; the score-only pass also takes 128-row entries, at half the
+                             arithmetic per K byte */
   const uint8_t* tile_uniform;   /* optional, uint8 [n_work, list_heads] from msa_list_uniformity: non-zero where all
                                     rows of a query tile carry the same page list (the tile's page set is then taken
                                     from one row instead of 128); NULL = no tile is assumed uniform */

@@ -204,6 +204,10 @@ def _fmha_sm100_plan(
                                 dense_kv_splits=n_split)[0]
             plan["work_split"] = torch.from_numpy(work_s).to(device).contiguous()
             plan["dense_kv_splits"] = n_split
+    if output_maxscore and not sparse:
+        # the score-only pass takes two query tiles per work item (every K page is fetched once for both)
+        work2 = _host_plan(qo_lens, kv_lens, off, causal, page_size > 0, num_qo_heads, num_kv_heads, tile_rows=256)[0]
+        plan["work_score"] = torch.from_numpy(work2).to(device).contiguous()
     plan["status"] = torch.zeros(1, dtype=torch.int32, device=device)
     plan["use_decode_kernel"] = bool(use_decode)
     plan["pack_factor"] = 1
@@ -311,7 +315,8 @@ def _run_prefill(q, k, v, plan, kv_indices, kv_block_indexes, qo_offset_t, out, 
     a.qk_dim = int(qk_dim)
     a.q, a.k, a.v = _ptr(q), _ptr(k), _ptr(v)
     a.out, a.lse, a.max_score = _ptr(out), _ptr(lse), _ptr(max_score)
-    work = plan["work"]
+    score_pairs = out is None and kv_block_indexes is None and "work_score" in plan
+    work = plan["work_score"] if score_pairs else plan["work"]
     n_split = 1
     if (out is not None and kv_block_indexes is None and "work_split" in plan
             and qo_offset_t is plan["qo_offset"]):
@@ -333,7 +338,7 @@ def _run_prefill(q, k, v, plan, kv_indices, kv_block_indexes, qo_offset_t, out, 
     if bool(is_paged) != (plan["page_size"] > 0):
         raise MsaError("the plan and the call disagree on paged vs ragged K/V (pass page_size to fmha_sm100_plan)")
     a.work, a.n_work = _ptr(work), int(work.shape[0])
-    a.tile_rows = 128
+    a.tile_rows = 256 if score_pairs else 128
     a.kv_indices = _ptr(kv_indices)
     a.kv_block_indexes = _ptr(kv_block_indexes)
     a.k_scale_128x4, a.v_scale_128x4 = _ptr(k_sf), _ptr(v_sf)

@@ -201,6 +201,22 @@ __device__ __forceinline__ void umma_ss_lohi(uint32_t d_tmem, uint32_t a_lo, uin
         : "memory");
   }
 }
+// e4m3 SS MMA whose operands use different descriptor high words (different swizzle modes / strides)
+template <int ACC>
+__device__ __forceinline__ void umma_ss_f8_lohi2(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                 uint32_t b_hi, uint32_t idesc) {
+  asm volatile(
+      "{\n"
+      ".reg .b64 da, db;\n"
+      ".reg .pred p;\n"
+      "mov.b64 da, {%1, %2};\n"
+      "mov.b64 db, {%3, %4};\n"
+      "setp.ne.b32 p, %6, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %5, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "n"(ACC)
+      : "memory");
+}
 __device__ __forceinline__ void umma_ts_lohi(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t hi,
                                              uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -219,6 +235,8 @@ __device__ __forceinline__ uint32_t smem_desc_lo(uint32_t saddr, uint32_t lbo_by
   return ((saddr & 0x3FFFFu) >> 4) | ((lbo_bytes >> 4) << 16);
 }
 __host__ __device__ constexpr uint32_t smem_desc_hi(uint32_t sbo_bytes) { return (sbo_bytes >> 4) | (1u << 14) | (2u << 29); }
+// same for rows of 64 bytes with the 64-byte swizzle (layout type 4)
+__host__ __device__ constexpr uint32_t smem_desc_hi_sw64(uint32_t sbo_bytes) { return (sbo_bytes >> 4) | (1u << 14) | (4u << 29); }
 
 // arrive on an mbarrier once every MMA issued so far by this thread has completed
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {

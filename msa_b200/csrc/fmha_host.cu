@@ -62,11 +62,15 @@ static int make_q_map(CUtensorMap* m, const void* q, int64_t total_q, int hq) {
 
 // K or V pages.  bf16: two 64-column SW128 boxes per tile.  e4m3: one 128-byte-row box, swizzled when the
 // tile feeds the tensor core as stored (K), plain when the convert warps read it (V).
-static int make_kv_map(CUtensorMap* m, const void* kv, int64_t rows, int hkv, int paged, int fp8, int fp8_swizzle) {
+// fp8_half: boxes over the first 64 bytes of every row only (score-only pass over a 64-wide slice), 64-byte swizzle.
+static int make_kv_map(CUtensorMap* m, const void* kv, int64_t rows, int hkv, int paged, int fp8, int fp8_swizzle,
+                       int fp8_half = 0) {
   const uint64_t es = fp8 ? 1 : 2;
   const CUtensorMapDataType dt = fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  const CUtensorMapSwizzle sw = (fp8 && !fp8_swizzle) ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B;
-  const uint32_t inner = fp8 ? 128 : 64;
+  const CUtensorMapSwizzle sw = (fp8 && fp8_half)       ? CU_TENSOR_MAP_SWIZZLE_64B
+                                : (fp8 && !fp8_swizzle) ? CU_TENSOR_MAP_SWIZZLE_NONE
+                                                        : CU_TENSOR_MAP_SWIZZLE_128B;
+  const uint32_t inner = fp8 ? (fp8_half ? 64 : 128) : 64;
   if (paged) {
     const uint64_t dims[4] = {128, 128, static_cast<uint64_t>(hkv), static_cast<uint64_t>(rows)};
     const uint64_t strides[3] = {128 * es, 128 * 128 * es, static_cast<uint64_t>(hkv) * 128 * 128 * es};
@@ -179,7 +183,8 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
   if (score_only && sparse) return MSA_ERR_UNSUPPORTED;        // the pass over page lists has no max-score output
   if (a->k_scale_format != 0 && (a->k_scale_format != 1 || !score_only || a->kv_dtype != MSA_KV_NVFP4))
     return MSA_ERR_INVALID;
-  if (a->tile_rows != 0 && a->tile_rows != 128) return MSA_ERR_INVALID;
+  if (a->tile_rows != 0 && a->tile_rows != 128 && a->tile_rows != 256) return MSA_ERR_INVALID;
+  if (a->tile_rows == 256 && !score_only) return MSA_ERR_UNSUPPORTED;
   if (a->n_work <= 0 || a->total_q <= 0) return MSA_OK;
   const int64_t out_rows = a->out_rows > 0 ? a->out_rows : a->total_q;
 
@@ -238,7 +243,7 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
     mv = mq;
   } else {
     const int fp8 = a->kv_dtype == MSA_KV_FP8_E4M3;
-    rc = make_kv_map(&mk, a->k, a->kv_rows, p.Hkv, a->paged, fp8, 1);
+    rc = make_kv_map(&mk, a->k, a->kv_rows, p.Hkv, a->paged, fp8, 1, fp8 && score_only && p.half_dim);
     if (rc != MSA_OK) return rc;
     rc = make_kv_map(&mv, a->v != nullptr ? a->v : a->k, a->kv_rows, p.Hkv, a->paged, fp8, 0);
     if (rc != MSA_OK) return rc;

@@ -3,21 +3,24 @@
 // (csrc/include/sm100_fmha_fwd_mainloop_tma_warpspecialized.hpp:842-1109, reached from
 // fmha_sm100(..., output_o=False, output_maxscore=True), python/fmha_sm100/api.py:1028).
 //
-// A kernel of its own because nothing of the attention kernel's structure fits it: there is no P, no V and no O, so
-// the only work besides the MMAs is one row maximum per (query row, page), and what bounds the loop is the
-// hand-over between the single MMA-issuing thread and the warps that read S.  Layout of one persistent CTA
-// (384 threads, one per SM, items = (128-row query tile, query head), heaviest first):
+// A kernel of its own because nothing of the attention kernel's structure fits it: there is no P, no V and no O.
+// The pass has little arithmetic per K byte (one 128 x 128 product per 16 KiB page and query tile), so with one query
+// tile per CTA the 148 SMs ask the L2 for more than it delivers; and one row maximum per (query row, page) is so
+// little work that the hand-over between the MMA-issuing thread and the warps that read S bounds the loop.  Hence:
 //
-//   warp 8     producer: Q of the next item into the other Q buffer, K pages two at a time into a ring of
-//              page PAIRS (the two pages of a pair lie back to back, so they form one 256-row operand)
-//   warp 9     MMA issuer: one tcgen05.mma per k-step with N = 256 covers both pages of a pair (half as many
-//              instructions, commits and barrier polls per page as N = 128); S pairs alternate between TMEM
-//              columns [0, 256) and [256, 512); tcgen05.commit releases the K pair and, after an item's last
-//              pair, the Q buffer
-//   warps 0-3  row-max warpgroup 0: thread = query row; reads the first page's 128 S columns of every pair,
-//   warps 4-7  row-max warpgroup 1: the second page's.  Both groups work on the SAME 128 query rows, so a pair of
-//              pages costs each of them one page of work while the tensor pipe needs two pages of time.
-//   warps 10-11 (NVFP4 / MXFP4 K only) dequantise raw pages into f16 operand tiles
+//   work item  256 query rows of one head (two 128-row tiles) against the pages its last row can see: every K
+//              page is fetched once for two tiles
+//   warp 8     producer: Q tiles of the item (of the NEXT item into the other buffer where shared memory allows
+//              two), K pages two at a time into a ring of page PAIRS (the two pages of a pair lie back to back,
+//              so they form one 256-row operand)
+//   warps 9,10 MMA issuers, one per tile: one tcgen05.mma per k-step with N = 256 covers both pages of a pair (half
+//              the instructions, commits and barrier polls per page of N = 128); tile t accumulates into TMEM
+//              columns [256 t, 256 t + 256); tcgen05.commit hands S to the row-max group, and -- one arrival per
+//              issuer -- releases the K pair and, after the item's last pair, the Q buffer.  (With packed e2m1 K
+//              warps 10-11 dequantise, and warp 9 issues for both tiles.)
+//   warps 0-3  row-max group of tile 0: thread = query row; S in 64-column chunks, two in flight; the buffer goes
+//   warps 4-7  back as soon as the last chunk has landed.  Same for tile 1.  While one tile's S is being read the
+//              tensor pipe works on the other tile.
 //
 // K formats: bf16 (TMA, 128-byte swizzle), e4m3 fed to kind::f8f6f4 as stored against a two-term e4m3 Q
 // (q = s (hi + lo), s a power of two per row), packed e2m1 with e4m3 (group 16) or ue8m0 (group 32) block scales
@@ -35,11 +38,21 @@ struct ScoreCfg {
   static constexpr bool kKConvert = KVMODE == KV_NVFP4;
   static constexpr int kPageBytes = kKDirectFp8 ? kHalfBytes : kTileBytes;   // one page as an MMA operand
   static constexpr int kPairBytes = 2 * kPageBytes;
-  static constexpr int kPairs = kKDirectFp8 ? 4 : 2;                         // ring depth: 128 KiB of K
+  // shared memory: two Q tiles per buffer (64 KiB); e4m3 K leaves room for two Q buffers and three pairs, the
+  // 16-bit operand formats for one Q buffer and two pairs (128 KiB)
+  static constexpr int kQBufs = kKDirectFp8 ? 2 : 1;
+  static constexpr int kPairs = 2;
+  // e4m3 K over a 64-element slice takes 8 KiB per page: the ring then holds five pairs in 80 KiB
+  static constexpr int kPairsHalf = 5;
+  static constexpr int kMaxPairs = kKDirectFp8 ? kPairsHalf : kPairs;
+  static constexpr int kRingBytes = kKDirectFp8 ? kPairsHalf * kPairBytes / 2 : kPairs * kPairBytes;
   static constexpr int kRawStages = kKConvert ? 3 : 0;
   static constexpr int kRawBytes = 8192 + 1024;                              // packed e2m1 page + its scales
   static constexpr int kThreads = 384;
   static constexpr int kProducerWarp = 8, kMmaWarp = 9, kCvtWarp0 = 10;
+  // One thread spends about as long polling barriers and committing as issuing; with an issuer per tile one of
+  // them is always feeding the pipe.  Warp 10 converts K in the e2m1 mode, which keeps a single issuer.
+  static constexpr int kIssuers = kKConvert ? 1 : 2;
   // 256 row-max threads at 216 registers + 128 helper threads at 72 = 384 x 168 (see FmhaCfg)
   static constexpr int kRegsLaunch = 168, kRegsRowMax = 216, kRegsHelper = 72;
   static_assert(256 * kRegsRowMax + 128 * kRegsHelper == 384 * kRegsLaunch, "setmaxnreg budget must balance");
@@ -49,14 +62,14 @@ struct ScoreCfg {
 template <int KVMODE>
 struct __align__(1024) ScoreSmem {
   using Cfg = ScoreCfg<KVMODE>;
-  uint8_t q[2][kTileBytes];
-  uint8_t k[Cfg::kPairs][Cfg::kPairBytes];
+  uint8_t q[Cfg::kQBufs][2][kTileBytes];
+  uint8_t k[Cfg::kRingBytes];
   uint8_t raw[Cfg::kRawStages > 0 ? Cfg::kRawStages : 1][Cfg::kRawStages > 0 ? Cfg::kRawBytes : 16];
-  float q_row_scale[2][128];   // e4m3 K: power-of-two scale of every rewritten Q row
-  uint64_t q_full[2], q_ready[2], q_empty[2];
-  uint64_t k_full[Cfg::kPairs], k_empty[Cfg::kPairs];
+  float q_row_scale[Cfg::kQBufs][2][128];   // e4m3 K: power-of-two scale of every rewritten Q row
+  uint64_t q_full[Cfg::kQBufs], q_ready[Cfg::kQBufs], q_empty[Cfg::kQBufs];
+  uint64_t k_full[Cfg::kMaxPairs], k_empty[Cfg::kMaxPairs];
   uint64_t raw_full[Cfg::kRawStages > 0 ? Cfg::kRawStages : 1], raw_empty[Cfg::kRawStages > 0 ? Cfg::kRawStages : 1];
-  uint64_t sc_full[2], sc_free[2];
+  uint64_t sc_full[2][2], sc_free[2][2];   // [tile][page of the pair]
   uint32_t tmem_base;
   int abort;
 };
@@ -66,9 +79,9 @@ constexpr int score_smem_bytes() {
   return static_cast<int>(sizeof(ScoreSmem<KVMODE>)) + 1024;
 }
 
-// One query tile x one head.
+// Up to 256 query rows of one head: tile 0 = rows [0, 128), tile 1 = rows [128, 256) of the work entry.
 struct ScoreItem {
-  int tok0, rows, qloc0, h, g, kv_len, qo_off, kv_base, n_pages;
+  int tok0, rows, qloc0, h, g, kv_len, qo_off, kv_base, n_pages, n_tiles;
 };
 
 __device__ __forceinline__ ScoreItem score_item(const FmhaParams& p, int item) {
@@ -83,7 +96,8 @@ __device__ __forceinline__ ScoreItem score_item(const FmhaParams& p, int item) {
   it.kv_len = w2.x;
   it.qo_off = w2.y;
   it.kv_base = w2.z;
-  int vis = it.kv_len;   // keys visible to the last row of the tile
+  it.n_tiles = it.rows > 128 ? 2 : 1;
+  int vis = it.kv_len;   // keys visible to the last row of the entry
   if (p.causal) vis = min(vis, it.qloc0 + it.rows + it.qo_off);
   it.n_pages = vis > 0 ? (vis + 127) >> 7 : 0;
   return it;
@@ -97,15 +111,21 @@ __device__ __forceinline__ void issue_score_qk(uint32_t q_saddr, uint32_t k_sadd
   if constexpr (Cfg::kKDirectFp8) {
     // Q_hi on the first 16 KiB of the Q tile, Q_lo on the second; 32 contraction bytes per step
     constexpr uint32_t idesc = make_idesc(128, N, 0, 0, 0, 0);
-    umma_ss_lohi<0, 1>(d, qa, ka, desc_hi, idesc);
-    umma_ss_lohi<1, 1>(d, qa + 2, ka + 2, desc_hi, idesc);
-    if (!half_dim) {
+    if (half_dim) {
+      // only the first 64 bytes of every K row were loaded: rows of 64 bytes under the 64-byte swizzle, eight of
+      // them 512 bytes apart
+      constexpr uint32_t k_hi = smem_desc_hi_sw64(512);
+      umma_ss_f8_lohi2<0>(d, qa, desc_hi, ka, k_hi, idesc);
+      umma_ss_f8_lohi2<1>(d, qa + 2, desc_hi, ka + 2, k_hi, idesc);
+      umma_ss_f8_lohi2<1>(d, qa + 1024, desc_hi, ka, k_hi, idesc);
+      umma_ss_f8_lohi2<1>(d, qa + 1026, desc_hi, ka + 2, k_hi, idesc);
+    } else {
+      umma_ss_lohi<0, 1>(d, qa, ka, desc_hi, idesc);
+      umma_ss_lohi<1, 1>(d, qa + 2, ka + 2, desc_hi, idesc);
       umma_ss_lohi<1, 1>(d, qa + 4, ka + 4, desc_hi, idesc);
       umma_ss_lohi<1, 1>(d, qa + 6, ka + 6, desc_hi, idesc);
-    }
-    umma_ss_lohi<1, 1>(d, qa + 1024, ka, desc_hi, idesc);
-    umma_ss_lohi<1, 1>(d, qa + 1026, ka + 2, desc_hi, idesc);
-    if (!half_dim) {
+      umma_ss_lohi<1, 1>(d, qa + 1024, ka, desc_hi, idesc);
+      umma_ss_lohi<1, 1>(d, qa + 1026, ka + 2, desc_hi, idesc);
       umma_ss_lohi<1, 1>(d, qa + 1028, ka + 4, desc_hi, idesc);
       umma_ss_lohi<1, 1>(d, qa + 1030, ka + 6, desc_hi, idesc);
     }
@@ -132,7 +152,7 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                  const FmhaParams p) {
   using Cfg = ScoreCfg<KVMODE>;
   using Smem = ScoreSmem<KVMODE>;
-  constexpr int NP = Cfg::kPairs;
+  constexpr int QB = Cfg::kQBufs;
   constexpr int NRAW = Cfg::kRawStages > 0 ? Cfg::kRawStages : 1;
   extern __shared__ uint8_t smem_raw[];
   Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -144,16 +164,20 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   MSA_TDECL
 
   if (tid == 0) {
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < QB; ++b) {
       mbar_init(&sm.q_full[b], 1);
       mbar_init(&sm.q_ready[b], 8);     // one arrival per row-max warp
-      mbar_init(&sm.q_empty[b], 1);
-      mbar_init(&sm.sc_full[b], 1);
-      mbar_init(&sm.sc_free[b], 8);
+      mbar_init(&sm.q_empty[b], Cfg::kIssuers);
     }
-    for (int s = 0; s < NP; ++s) {
+    for (int t = 0; t < 2; ++t) {
+      for (int e = 0; e < 2; ++e) {
+        mbar_init(&sm.sc_full[t][e], 1);
+        mbar_init(&sm.sc_free[t][e], 4);     // the four warps of the tile's row-max group
+      }
+    }
+    for (int s = 0; s < Cfg::kMaxPairs; ++s) {
       mbar_init(&sm.k_full[s], Cfg::kKConvert ? 2 : 1);
-      mbar_init(&sm.k_empty[s], 1);
+      mbar_init(&sm.k_empty[s], Cfg::kIssuers);
     }
     for (int s = 0; s < NRAW; ++s) {
       mbar_init(&sm.raw_full[s], 1);
@@ -195,83 +219,88 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       if (it.n_pages > 0) return true;
     }
   };
+  // e4m3 K over the first 64 head-dim elements only: the TMA box is 64 bytes wide, a page takes 8 KiB
+  const bool fp8_half = Cfg::kKDirectFp8 && p.half_dim != 0;
+  const uint32_t page_stride = fp8_half ? kHalfBytes / 2 : kHalfBytes;   // second page: rows 128-255 of the operand
+  const int NP = fp8_half ? Cfg::kPairsHalf : Cfg::kPairs;               // pairs in the K ring
+  const uint32_t pair_bytes = fp8_half ? Cfg::kPairBytes / 2 : Cfg::kPairBytes;
 
   if (warp < 8) {
     // =========================================================================
-    // row-max warpgroup w: the w-th page of every pair
+    // row-max group of tile t
     // =========================================================================
     setmaxnreg_inc<Cfg::kRegsRowMax>();
-    const int w = warp >> 2;
+    const int t = warp >> 2;
     const int r = tid & 127;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t s_cur = tmem + lane_base + t * 256;
     bool ok = true;
-    uint32_t pair_seq = 0, n_q = 0;
+    uint32_t use_a = 0, use_b = 0;   // first / second pages of my tile so far (sc_full / sc_free phases)
+    uint32_t n_q = 0;
 
-    // Q of item number n_q (buffer n_q & 1) into the operand format of the quantised modes.  Rows 0-63 are
-    // rewritten by warps 0-1 of group 0, rows 64-127 by warps 2-3 of group 1; every warp arrives.
-    auto convert_q = [&](uint32_t nq) {
+    // My tile of Q item number nq (buffer nq % QB) into the operand format of the quantised modes; every warp
+    // arrives, also when its tile does not exist.
+    auto convert_q = [&](uint32_t nq, int n_tiles) {
       if constexpr (Cfg::kQuant) {
-        const int qb = nq & 1;
-        ok = ok && mbar_wait(&sm.q_full[qb], (nq >> 1) & 1, abort_flag);
-        if (ok) {
+        const int qb = nq % QB;
+        ok = ok && mbar_wait(&sm.q_full[qb], (nq / QB) & 1, abort_flag);
+        if (ok && t < n_tiles) {
           if constexpr (Cfg::kKDirectFp8) {
-            if ((r >> 6) == w) {
-              // my row -> two e4m3 rows (hi, lo) sharing one power-of-two scale; hi lands on the first
-              // 64-column half of the bf16 tile, lo on the second, same row: in place, thread-private
-              uint8_t* rowp = sm.q[qb] + r * 128;
-              uint4 x[16];
+            // my row -> two e4m3 rows (hi, lo) sharing one power-of-two scale; hi lands on the first
+            // 64-column half of the bf16 tile, lo on the second, same row: in place, thread-private
+            uint8_t* rowp = sm.q[qb][t] + r * 128;
+            uint4 x[16];
 #pragma unroll
-              for (int c = 0; c < 16; ++c)
-                x[c] = *reinterpret_cast<const uint4*>(rowp + (c >> 3) * kHalfBytes + (((c & 7) ^ (r & 7)) << 4));
-              float amax = 0.f;
+            for (int c = 0; c < 16; ++c)
+              x[c] = *reinterpret_cast<const uint4*>(rowp + (c >> 3) * kHalfBytes + (((c & 7) ^ (r & 7)) << 4));
+            float amax = 0.f;
 #pragma unroll
-              for (int c = 0; c < 16; ++c) {
-                const uint32_t v[4] = {x[c].x, x[c].y, x[c].z, x[c].w};
+            for (int c = 0; c < 16; ++c) {
+              const uint32_t v[4] = {x[c].x, x[c].y, x[c].z, x[c].w};
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  amax = fmaxf(amax, fabsf(__uint_as_float(v[i] << 16)));
-                  amax = fmaxf(amax, fabsf(__uint_as_float(v[i] & 0xffff0000u)));
+              for (int i = 0; i < 4; ++i) {
+                amax = fmaxf(amax, fabsf(__uint_as_float(v[i] << 16)));
+                amax = fmaxf(amax, fabsf(__uint_as_float(v[i] & 0xffff0000u)));
+              }
+            }
+            float sq = 1.0f;   // power of two that brings the row maximum into [224, 448]
+            if (amax > 0.f && amax < 3.0e38f) {
+              int e;
+              frexpf(amax, &e);
+              sq = ldexpf(1.0f, e - 9);
+              if (amax / sq > 448.0f) sq *= 2.0f;
+            }
+            const float inv = 1.0f / sq;
+            sm.q_row_scale[qb][t][r] = sq;
+#pragma unroll
+            for (int c8 = 0; c8 < 8; ++c8) {
+              uint32_t hi4[4], lo4[4];
+#pragma unroll
+              for (int half = 0; half < 2; ++half) {
+                const uint4 xv = x[c8 * 2 + half];
+                const uint32_t v[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+                for (int i = 0; i < 4; i += 2) {
+                  float y[4] = {__uint_as_float(v[i] << 16) * inv, __uint_as_float(v[i] & 0xffff0000u) * inv,
+                                __uint_as_float(v[i + 1] << 16) * inv, __uint_as_float(v[i + 1] & 0xffff0000u) * inv};
+                  const uint32_t h01 = f32x2_to_e4m3x2(y[0], y[1]), h23 = f32x2_to_e4m3x2(y[2], y[3]);
+                  float f[4];
+                  e4m3x2_to_f32x2(h01, f[0], f[1]);
+                  e4m3x2_to_f32x2(h23, f[2], f[3]);
+                  const uint32_t l01 = f32x2_to_e4m3x2(y[0] - f[0], y[1] - f[1]);
+                  const uint32_t l23 = f32x2_to_e4m3x2(y[2] - f[2], y[3] - f[3]);
+                  hi4[half * 2 + (i >> 1)] = h01 | (h23 << 16);
+                  lo4[half * 2 + (i >> 1)] = l01 | (l23 << 16);
                 }
               }
-              float sq = 1.0f;   // power of two that brings the row maximum into [224, 448]
-              if (amax > 0.f && amax < 3.0e38f) {
-                int e;
-                frexpf(amax, &e);
-                sq = ldexpf(1.0f, e - 9);
-                if (amax / sq > 448.0f) sq *= 2.0f;
-              }
-              const float inv = 1.0f / sq;
-              sm.q_row_scale[qb][r] = sq;
-#pragma unroll
-              for (int c8 = 0; c8 < 8; ++c8) {
-                uint32_t hi4[4], lo4[4];
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                  const uint4 xv = x[c8 * 2 + half];
-                  const uint32_t v[4] = {xv.x, xv.y, xv.z, xv.w};
-#pragma unroll
-                  for (int i = 0; i < 4; i += 2) {
-                    float y[4] = {__uint_as_float(v[i] << 16) * inv, __uint_as_float(v[i] & 0xffff0000u) * inv,
-                                  __uint_as_float(v[i + 1] << 16) * inv, __uint_as_float(v[i + 1] & 0xffff0000u) * inv};
-                    const uint32_t h01 = f32x2_to_e4m3x2(y[0], y[1]), h23 = f32x2_to_e4m3x2(y[2], y[3]);
-                    float f[4];
-                    e4m3x2_to_f32x2(h01, f[0], f[1]);
-                    e4m3x2_to_f32x2(h23, f[2], f[3]);
-                    const uint32_t l01 = f32x2_to_e4m3x2(y[0] - f[0], y[1] - f[1]);
-                    const uint32_t l23 = f32x2_to_e4m3x2(y[2] - f[2], y[3] - f[3]);
-                    hi4[half * 2 + (i >> 1)] = h01 | (h23 << 16);
-                    lo4[half * 2 + (i >> 1)] = l01 | (l23 << 16);
-                  }
-                }
-                const uint32_t off = ((c8 ^ (r & 7)) << 4);
-                *reinterpret_cast<uint4*>(rowp + off) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
-                *reinterpret_cast<uint4*>(rowp + kHalfBytes + off) = make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]);
-              }
+              const uint32_t off = ((c8 ^ (r & 7)) << 4);
+              *reinterpret_cast<uint4*>(rowp + off) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
+              *reinterpret_cast<uint4*>(rowp + kHalfBytes + off) = make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]);
             }
           } else {
             // bf16 -> f16 in place (the dequantised K tiles are f16 and the tensor core wants one format)
-            uint4* qv = reinterpret_cast<uint4*>(sm.q[qb]);
-            for (int i = w * 128 + r; i < kTileBytes / 16; i += 256) {
+            uint4* qv = reinterpret_cast<uint4*>(sm.q[qb][t]);
+            for (int i = r; i < kTileBytes / 16; i += 128) {
               uint4 xq = qv[i];
               xq.x = bf16x2_to_f16x2(xq.x);
               xq.y = bf16x2_to_f16x2(xq.y);
@@ -290,76 +319,104 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     int j = 0, j_next = 0;
     ScoreItem it, it_next;
     bool have = next_item(j, it);
-    if (have) convert_q(0);
+    if (have && QB == 2) convert_q(0, it.n_tiles);
     while (have && ok) {
       j_next = j + 1;
       const bool have_next = next_item(j_next, it_next);
-      const bool row_valid = r < it.rows;
+      if (QB == 1) convert_q(n_q, it.n_tiles);   // a single Q buffer: rewritten when the item starts
+      const int r_tile = t * 128 + r;            // my row within the work entry
+      const bool row_valid = r_tile < it.rows;
       int limit_base = -1;
       if (row_valid) {
         limit_base = it.kv_len - 1;
-        if (p.causal) limit_base = min(limit_base, it.qloc0 + r + it.qo_off);
+        if (p.causal) limit_base = min(limit_base, it.qloc0 + r_tile + it.qo_off);
       }
       float row_scale = 1.0f;
-      float* dst = p.max_score + static_cast<long long>(it.h) * p.ms_head + it.tok0 + r;
+      float* dst = p.max_score + static_cast<long long>(it.h) * p.ms_head + it.tok0 + r_tile;
       const int n = it.n_pages, n_pairs = (n + 1) >> 1;
-      for (int pi = 0; pi < n_pairs && ok; ++pi, ++pair_seq) {
-        const int sb = pair_seq & 1;
-        MSA_TBEGIN
-        ok = mbar_wait(&sm.sc_full[sb], (pair_seq >> 1) & 1, abort_flag);
-        MSA_TEND(0)
-        if (!ok) break;
-        tc_fence_after();
-        if (r == 0) { MSA_TRACE(w * 2, pair_seq, clock64()) }
-        MSA_TBEGIN
-        const int page = n - 1 - (2 * pi + w);   // pages are walked from the highest down
-        if (page >= 0) {
+      const bool mine = t < it.n_tiles;
+      for (int pi = 0; pi < n_pairs && ok; ++pi) {
+        if (mine) {
+          const int page_a = n - 1 - 2 * pi, page_b = page_a - 1;   // pages are walked from the highest down
+          const bool two = page_b >= 0;
+          MSA_TBEGIN
+          ok = mbar_wait(&sm.sc_full[t][0], use_a & 1, abort_flag);
+          MSA_TEND(0)
+          if (!ok) break;
+          ++use_a;
+          tc_fence_after();
+          if (r == 0) { MSA_TRACE(t * 2, use_a, clock64()) }
+          MSA_TBEGIN
           if constexpr (Cfg::kKDirectFp8) {
-            if (pi == 0) row_scale = sm.q_row_scale[n_q & 1][r];
+            if (pi == 0) row_scale = sm.q_row_scale[n_q % QB][t][r];
           }
-          uint32_t sr[128];
-          const uint32_t s_cur = tmem + lane_base + sb * 256 + w * 128;
-          tmem_ld32p(s_cur, sr);
-          tmem_ld32p(s_cur + 32, sr + 32);
-          tmem_ld32p(s_cur + 64, sr + 64);
-          tmem_ld32p(s_cur + 96, sr + 96);
+          // 64-column chunks, two in flight: c0, c1 = first page, then second.  A chunk's registers take the next
+          // load as soon as its maxima are folded in; each page's columns go back to the issuer as soon as they
+          // are in registers, so the next pair's MMAs for the first page run while the second is being read.
+          uint32_t c0[64], c1[64];
+          tmem_ld32p(s_cur, c0);
+          tmem_ld32p(s_cur + 32, c0 + 32);
+          tmem_ld32p(s_cur + 64, c1);
+          tmem_ld32p(s_cur + 96, c1 + 32);
           tmem_ld_wait();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&sm.sc_free[sb]);   // S is in registers: the MMA warp may overwrite it
-          const int limit = limit_base - (page << 7);
-          if (!__all_sync(0xffffffffu, limit >= 127)) {
+          if (lane == 0) mbar_arrive(&sm.sc_free[t][0]);
+          const int limit_a = limit_base - (page_a << 7), limit_b = limit_a + 128;
+          const bool vis_a = __all_sync(0xffffffffu, limit_a >= 127);
+          auto fold = [&](uint32_t (&c)[64], int lim, bool all_visible, float& m0, float& m1, float& m2, float& m3) {
+            if (!all_visible) {
 #pragma unroll
-            for (int c = 0; c < 128; ++c) sr[c] = (c <= limit) ? sr[c] : 0xff800000u;
-          }
-          float t0 = -INFINITY, t1 = -INFINITY, t2 = -INFINITY, t3 = -INFINITY;
+              for (int e = 0; e < 64; ++e) c[e] = (e <= lim) ? c[e] : 0xff800000u;
+            }
 #pragma unroll
-          for (int c = 0; c < 128; c += 8) {
-            t0 = max3(t0, __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
-            t1 = max3(t1, __uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3]));
-            t2 = max3(t2, __uint_as_float(sr[c + 4]), __uint_as_float(sr[c + 5]));
-            t3 = max3(t3, __uint_as_float(sr[c + 6]), __uint_as_float(sr[c + 7]));
+            for (int e = 0; e < 64; e += 8) {
+              m0 = max3(m0, __uint_as_float(c[e]), __uint_as_float(c[e + 1]));
+              m1 = max3(m1, __uint_as_float(c[e + 2]), __uint_as_float(c[e + 3]));
+              m2 = max3(m2, __uint_as_float(c[e + 4]), __uint_as_float(c[e + 5]));
+              m3 = max3(m3, __uint_as_float(c[e + 6]), __uint_as_float(c[e + 7]));
+            }
+          };
+          float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;
+          fold(c0, limit_a, vis_a, a0, a1, a2, a3);
+          if (two) {
+            ok = mbar_wait(&sm.sc_full[t][1], use_b & 1, abort_flag);
+            if (!ok) break;
+            ++use_b;
+            tc_fence_after();
+            tmem_ld32p(s_cur + 128, c0);
+            tmem_ld32p(s_cur + 160, c0 + 32);
           }
-          const float tmax = fmaxf(fmaxf(t0, t1), fmaxf(t2, t3));
-          if (row_valid) __stwt(dst + static_cast<long long>(page) * p.ms_tile, tmax * row_scale);
-        } else {
-          // the last pair of an odd walk has no second page: nothing to read, but the buffer still takes my arrival
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&sm.sc_free[sb]);
+          fold(c1, limit_a - 64, vis_a, a0, a1, a2, a3);
+          if (row_valid)
+            __stwt(dst + static_cast<long long>(page_a) * p.ms_tile, fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) * row_scale);
+          if (two) {
+            tmem_ld32p(s_cur + 192, c1);
+            tmem_ld32p(s_cur + 224, c1 + 32);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.sc_free[t][1]);
+            const bool vis_b = __all_sync(0xffffffffu, limit_b >= 127);
+            float b0 = -INFINITY, b1 = -INFINITY, b2 = -INFINITY, b3 = -INFINITY;
+            fold(c0, limit_b, vis_b, b0, b1, b2, b3);
+            fold(c1, limit_b - 64, vis_b, b0, b1, b2, b3);
+            if (row_valid)
+              __stwt(dst + static_cast<long long>(page_b) * p.ms_tile, fmaxf(fmaxf(b0, b1), fmaxf(b2, b3)) * row_scale);
+          }
+          MSA_TEND(1)
         }
-        MSA_TEND(1)
-        // Q of the next item is rewritten while the MMA warp still has this item's pairs in hand.  The producer
-        // issues that Q load right after K pair min(1, n_pairs - 1) of this item (see there), so waiting for it at
-        // the same pair cannot dead-lock: the ring holds at least two pairs.
-        if (pi == min(1, n_pairs - 1) && have_next) convert_q(n_q + 1);
+        // Two Q buffers: Q of the next item is rewritten while the issuers still have this item's pairs in hand.
+        // The producer issues that Q load right after K pair min(1, n_pairs - 1) of this item (see there), so
+        // waiting for it at the same pair cannot dead-lock: the ring holds at least two pairs.
+        if (QB == 2 && pi == min(1, n_pairs - 1) && have_next) convert_q(n_q + 1, it_next.n_tiles);
       }
       ++n_q;
       have = have_next;
       it = it_next;
       j = j_next;
     }
-    MSA_TFLUSH(r == 0 && w == 0, 0, 3)
+    MSA_TFLUSH(r == 0 && t == 0, 0, 3)
   } else {
     setmaxnreg_dec<Cfg::kRegsHelper>();
     if (warp == Cfg::kProducerWarp) {
@@ -369,25 +426,29 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       if (lane == 0) {
         bool ok = true;
         uint32_t n_q = 0, pair_seq = 0, raw_seq = 0;
-        // Q of the item numbered n_q into buffer n_q & 1, once the item that used the buffer two items ago is done
+        // the Q tiles of the item numbered n_q into buffer n_q % QB, once the item that last used the buffer is done
         auto load_q = [&](const ScoreItem& qi) {
-          const int qb = n_q & 1;
+          const int qb = n_q % QB;
           MSA_TBEGIN
-          ok = mbar_wait(&sm.q_empty[qb], ((n_q >> 1) & 1) ^ 1, abort_flag);
+          ok = mbar_wait(&sm.q_empty[qb], ((n_q / QB) & 1) ^ 1, abort_flag);
           MSA_TEND(12)
           if (!ok) return;
           ++n_q;
-          mbar_expect_tx(&sm.q_full[qb], kTileBytes);
-          tma_load_3d(sm.q[qb], &tmap_q, &sm.q_full[qb], 0, qi.h, qi.tok0);
-          tma_load_3d(sm.q[qb] + kHalfBytes, &tmap_q, &sm.q_full[qb], 64, qi.h, qi.tok0);
+          mbar_expect_tx(&sm.q_full[qb], qi.n_tiles * kTileBytes);
+          for (int t = 0; t < qi.n_tiles; ++t) {
+            tma_load_3d(sm.q[qb][t], &tmap_q, &sm.q_full[qb], 0, qi.h, qi.tok0 + t * 128);
+            tma_load_3d(sm.q[qb][t] + kHalfBytes, &tmap_q, &sm.q_full[qb], 64, qi.h, qi.tok0 + t * 128);
+          }
         };
         int j = 0, j_next = 0;
         ScoreItem it, it_next;
         bool have = next_item(j, it);
-        if (have) load_q(it);
+        if (have && QB == 2) load_q(it);
         while (have && ok) {
           j_next = j + 1;
           const bool have_next = next_item(j_next, it_next);
+          if (QB == 1) load_q(it);
+          if (!ok) break;
           const int n = it.n_pages, n_pairs = (n + 1) >> 1;
           const int page_base = p.paged ? it.kv_base : 0;
           const int tok_base = p.paged ? 0 : it.kv_base;
@@ -414,12 +475,12 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
               ok = mbar_wait(&sm.k_empty[kq], ((pair_seq / NP) & 1) ^ 1, abort_flag);
               MSA_TEND(13)
               if (!ok) break;
-              mbar_expect_tx(&sm.k_full[kq], np * Cfg::kPageBytes);
+              mbar_expect_tx(&sm.k_full[kq], np * (fp8_half ? Cfg::kPageBytes / 2 : Cfg::kPageBytes));
               for (int e = 0; e < np; ++e) {
                 const int page = n - 1 - (2 * pi + e);
                 const int phys = p.paged ? __ldg(p.kv_indices + page_base + page) : 0;
                 const int tok_k = tok_base + (page << 7);
-                uint8_t* kdst = sm.k[kq] + e * kHalfBytes;   // second page: rows 128-255 of the operand
+                uint8_t* kdst = sm.k + kq * pair_bytes + e * page_stride;
                 if constexpr (Cfg::kKDirectFp8) {
                   if (p.paged)
                     tma_load_4d(kdst, &tmap_k, &sm.k_full[kq], 0, 0, it.g, phys);
@@ -434,8 +495,8 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 }
               }
             }
-            // the next item's Q goes out early, so that the row-max warps can rewrite it inside this item
-            if (ok && pi == min(1, n_pairs - 1) && have_next) load_q(it_next);
+            // two Q buffers: the next item's Q goes out early, so that it can be rewritten inside this item
+            if (QB == 2 && ok && pi == min(1, n_pairs - 1) && have_next) load_q(it_next);
           }
           have = have_next;
           it = it_next;
@@ -443,50 +504,69 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
         MSA_TFLUSH(true, 12, 14)
       }
-    } else if (warp == Cfg::kMmaWarp) {
+    } else if (warp == Cfg::kMmaWarp || (Cfg::kIssuers == 2 && warp == Cfg::kCvtWarp0)) {
       // =======================================================================
-      // MMA issuer
+      // MMA issuer: tile `me` with two issuers, both tiles with one.  tcgen05.commit covers the MMAs of the
+      // committing thread only, hence K pairs and Q buffers are released by one arrival per issuer.
       // =======================================================================
+      const int me = warp == Cfg::kMmaWarp ? 0 : 1;
       bool ok = true;
       uint32_t n_q = 0, pair_seq = 0;
+      uint32_t use_seq[2][2] = {{0, 0}, {0, 0}};   // pages issued per tile and page of the pair (sc_free phase)
       int j = 0;
       ScoreItem it;
       while (ok && next_item(j, it)) {
-        const int qb = n_q & 1;
+        const int qb = n_q % QB;
         MSA_TBEGIN
-        ok = mbar_wait(Cfg::kQuant ? &sm.q_ready[qb] : &sm.q_full[qb], (n_q >> 1) & 1, abort_flag);
+        ok = mbar_wait(Cfg::kQuant ? &sm.q_ready[qb] : &sm.q_full[qb], (n_q / QB) & 1, abort_flag);
         MSA_TEND(14)
         if (!ok) break;
         ++n_q;
-        const uint32_t qaddr = smem_u32(sm.q[qb]);
         const int n = it.n_pages, n_pairs = (n + 1) >> 1;
         for (int pi = 0; pi < n_pairs && ok; ++pi, ++pair_seq) {
           const int np = min(2, n - 2 * pi);
-          const int kq = pair_seq % NP, sb = pair_seq & 1;
+          const int kq = pair_seq % NP;
           MSA_TBEGIN
           ok = mbar_wait(&sm.k_full[kq], (pair_seq / NP) & 1, abort_flag);
           MSA_TEND(6)
-          MSA_TBEGIN
-          if (ok && pair_seq >= 2) ok = mbar_wait(&sm.sc_free[sb], ((pair_seq >> 1) + 1) & 1, abort_flag);
-          MSA_TEND(4)
           if (!ok) break;
-          tc_fence_after();
-          MSA_TBEGIN
+          const uint32_t kaddr = smem_u32(sm.k + kq * pair_bytes);
+#pragma unroll
+          for (int t = me; t < 2; t += Cfg::kIssuers) {
+            if (t < it.n_tiles) {
+              const uint32_t qaddr = smem_u32(sm.q[qb][t]);
+              // one page at a time (N = 128), each into its own 128 columns with its own barrier pair, so that the
+              // row-max group reads the first page while the second is computed
+              for (int e = 0; e < np && ok; ++e) {
+                MSA_TBEGIN
+                if (use_seq[t][e] >= 1) ok = mbar_wait(&sm.sc_free[t][e], (use_seq[t][e] + 1) & 1, abort_flag);
+                MSA_TEND(4)
+                if (!ok) break;
+                ++use_seq[t][e];
+                tc_fence_after();
+                MSA_TBEGIN
+                if (lane == 0) {
+                  issue_score_qk<Cfg, 128>(qaddr, kaddr + e * page_stride, t * 256 + e * 128, p.half_dim != 0);
+                  umma_commit(&sm.sc_full[t][e]);
+                }
+                __syncwarp();
+                MSA_TEND(5)
+              }
+            }
+          }
+          if (!ok) break;
           if (lane == 0) {
-            const uint32_t kaddr = smem_u32(sm.k[kq]);
-            if (np == 2) issue_score_qk<Cfg, 256>(qaddr, kaddr, sb * 256, p.half_dim != 0);
-            else issue_score_qk<Cfg, 128>(qaddr, kaddr, sb * 256, p.half_dim != 0);
-            umma_commit(&sm.sc_full[sb]);
-            umma_commit(&sm.k_empty[kq]);                       // the pair is free once these MMAs have read it
-            if (pi + 1 == n_pairs) umma_commit(&sm.q_empty[qb]);  // and Q after the item's last pair
+            // my share of the K pair (and of Q after the item's last pair): freed when my MMAs above have read
+            // it -- at once if I had no tile to issue for
+            umma_commit(&sm.k_empty[kq]);
+            if (pi + 1 == n_pairs) umma_commit(&sm.q_empty[qb]);
           }
           __syncwarp();
-          MSA_TEND(5)
         }
         ++j;
       }
-      MSA_TFLUSH(lane == 0, 4, 7)
-      MSA_TFLUSH(lane == 0, 14, 15)
+      MSA_TFLUSH(lane == 0 && me == 0, 4, 7)
+      MSA_TFLUSH(lane == 0 && me == 0, 14, 15)
     } else if constexpr (Cfg::kKConvert) {
       // =======================================================================
       // dequantise raw e2m1 pages into f16 operand tiles (64 threads; a thread owns one 16-value block of every
@@ -511,7 +591,7 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             ok = mbar_wait(&sm.raw_full[rs], (raw_seq / NRAW) & 1, abort_flag);
             if (!ok) break;
             const uint8_t* rawp = sm.raw[rs];
-            uint8_t* dst = sm.k[kq] + e * kHalfBytes + (c8 >> 2) * kTileBytes + r8 * 128;
+            uint8_t* dst = sm.k + kq * pair_bytes + e * kHalfBytes + (c8 >> 2) * kTileBytes + r8 * 128;
             const uint8_t* src = rawp + ct * 8;
             // scale of (row, block): 128x4 tile offset (row % 32) * 16 + (row / 32) * 4 + block % 4; with ue8m0
             // scales a block of 16 values shares the scale of its group of 32 (block c8 -> group c8 / 2)
