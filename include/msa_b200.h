@@ -216,6 +216,30 @@ int msa_fmha_combine(const void* partial_out, const float* partial_lse, int32_t 
 int msa_list_uniformity(const int32_t* work, int32_t n_work, const int32_t* kv_block_indexes, int32_t list_heads,
                         int32_t topk, uint8_t* flags, void* stream);
 
+/* FP4 indexer (fp4_indexer_block_scores, python/fmha_sm100/cute/fp4_indexer_interface.py:745-1056): per-page maxima
+ * of Q K^T with Q and K given as packed e2m1 (two values per byte, low nibble = even element) and block scales.
+ * The scores come from msa_fmha_fwd in its score-only form (out = NULL) with kv_dtype = MSA_KV_NVFP4, k = the packed
+ * pages [pages, num_kv_heads, 128, 64], k_scale_128x4 = the K scales in 128x4-tiled storage (one 1024- or 512-byte
+ * block per (page, head)), k_scale_format = the format below, and q = Q dequantised to bf16 by
+ * msa_fp4_dequant_rows (exact: e2m1 times a block scale has at most six significant bits).
+ *   format        0: NVFP4, one e4m3 scale per 16 values (8 per row); 1: MXFP4, one ue8m0 scale per 32 (4 per row)
+ *   scale_layout  0: logical [rows, heads, G]; 1: 128x4-tiled storage with mn = rows, l = heads
+ *                 (fp4_indexer_mma_scale_storage_shape, fp4_indexer_interface.py:236-249)
+ *   packed uint8 [rows, heads, 64]; out bf16 [rows, heads, 128]. */
+#define MSA_FP4_NVFP4 0
+#define MSA_FP4_MXFP4 1
+int msa_fp4_dequant_rows(const void* packed, const void* scales, int32_t format, int32_t scale_layout, int64_t rows,
+                         int32_t heads, void* out, void* stream);
+
+/* Logical scales -> 128x4-tiled storage (Fp4IndexerScaleReorderSm100,
+ * python/fmha_sm100/cute/src/sm100/fp4_indexer.py:83-199): element (m, g, l) goes to
+ * l * 512 * ceil(mn / 128) * ceil(G / 4) + (m / 128) * 512 * ceil(G / 4) + (g / 4) * 512 + (m % 32) * 16
+ * + ((m % 128) / 32) * 4 + g % 4.  k_layout = 1: src is [l_extent, mn, G] (K scales, mn = 128, l = page * heads +
+ * head); k_layout = 0: src is [mn, l_extent, G] (Q scales, mn = tokens, l = head).  dst holds
+ * l_extent * ceil(mn / 128) * ceil(G / 4) * 512 bytes; bytes of rows beyond mn are left untouched. */
+int msa_fp4_reorder_scales(const void* src, int32_t format, int64_t mn, int64_t l_extent, int32_t k_layout, void* dst,
+                           void* stream);
+
 /* k2q CSR -> per-query page lists, on the device.  The reference's sparse prefill is KV-outer and consumes the
  * reverse index built by `build_k2q_csr` (python/fmha_sm100/cute/sparse_index_utils.py:331-420,
  * python/fmha_sm100/cute/src/sm100/prepare_k2q_csr.py:54); the kernel here is query-stationary, so the

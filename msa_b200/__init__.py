@@ -6,6 +6,10 @@ from .quant import (Nvfp4QuantizedTensor, dequantize_nvfp4_128x4, quantize_bf16_
 from .sparse import (SparseDecodePagedAttentionWrapper, build_k2q_csr, k2q_csr_to_lists, k2q_csr_to_q2k,  # noqa: F401
                      sparse_atten_func, sparse_atten_nvfp4_kv_func, sparse_decode_atten_func, sparse_prefill_nvfp4)
 from .host_pipeline import HostPrefillPipeline  # noqa: F401
+from .fp4_indexer import (fp4_indexer_block_scores, fp4_indexer_mma_scale_shape,  # noqa: F401
+                          fp4_indexer_mma_scale_storage_shape, fp4_indexer_mma_scale_storage_stride,
+                          fp4_indexer_mma_scale_stride, fp4_indexer_reorder_scales_for_mma,
+                          fp4_indexer_reorder_scales_for_mma_cute)
 from .kv_cache import absmax_bf16, append_kv_fp8, append_kv_nvfp4  # noqa: F401
 from .shard import (gather_heads, head_shard, request_cost, scatter_rows, shard_batch, shard_kv_heads,  # noqa: F401
                     shard_requests)

@@ -17,7 +17,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 # MSA_B200_LIB points the loader at another build of the same ABI (e.g. one made with -DMSA_ROLE_TIMING)
 LIB_PATH = os.environ.get("MSA_B200_LIB") or os.path.join(_HERE, "libmsa_b200.so")
 CSRC = os.path.join(_HERE, "csrc")
-SOURCES = ["abi.cu", "topk.cu", "decode.cu", "fmha_host.cu", "kv_quant.cu", "plan_host.cu", "csr.cu"]
+SOURCES = ["abi.cu", "topk.cu", "decode.cu", "fmha_host.cu", "kv_quant.cu", "plan_host.cu", "csr.cu", "fp4_indexer.cu"]
 
 MSA_KV_BF16, MSA_KV_FP8_E4M3, MSA_KV_NVFP4 = 0, 1, 2
 MSA_ERR_TIMEOUT = -3
@@ -168,6 +168,10 @@ def _bind(lib):
     lib.msa_block_max.argtypes = [vp, c_int32, c_int32, c_int32, vp, c_int32, vp, vp]
     lib.msa_fmha_combine.restype = c_int32
     lib.msa_fmha_combine.argtypes = [vp, vp, c_int32, c_int64, c_int32, vp, vp, vp]
+    lib.msa_fp4_dequant_rows.restype = c_int32
+    lib.msa_fp4_dequant_rows.argtypes = [vp, vp, c_int32, c_int32, c_int64, c_int32, vp, vp]
+    lib.msa_fp4_reorder_scales.restype = c_int32
+    lib.msa_fp4_reorder_scales.argtypes = [vp, c_int32, c_int64, c_int64, c_int32, vp, vp]
     lib.msa_list_uniformity.restype = c_int32
     lib.msa_list_uniformity.argtypes = [vp, c_int32, vp, c_int32, c_int32, vp, vp]
     lib.msa_fmha_fwd.restype = c_int32

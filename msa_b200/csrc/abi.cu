@@ -67,6 +67,17 @@ int msa_block_max(const float* max_score, int32_t num_heads, int32_t max_k_tiles
                         static_cast<cudaStream_t>(stream));
 }
 
+int msa_fp4_dequant_rows(const void* packed, const void* scales, int32_t format, int32_t scale_layout, int64_t rows,
+                         int32_t heads, void* out, void* stream) {
+  return msa::fp4_dequant_rows(packed, scales, format, scale_layout, rows, heads, out,
+                               static_cast<cudaStream_t>(stream));
+}
+
+int msa_fp4_reorder_scales(const void* src, int32_t format, int64_t mn, int64_t l_extent, int32_t k_layout, void* dst,
+                           void* stream) {
+  return msa::fp4_reorder_scales(src, format, mn, l_extent, k_layout, dst, static_cast<cudaStream_t>(stream));
+}
+
 int msa_list_uniformity(const int32_t* work, int32_t n_work, const int32_t* kv_block_indexes, int32_t list_heads,
                         int32_t topk, uint8_t* flags, void* stream) {
   return msa::list_uniformity(work, n_work, kv_block_indexes, list_heads, topk, flags,

@@ -49,6 +49,10 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st);
 void set_timing_buffer(void* ptr);
 int fmha_combine(const void* partial_out, const float* partial_lse, int n_splits, int64_t total_q, int num_qo_heads,
                  void* out, float* lse, cudaStream_t st);
+int fp4_dequant_rows(const void* packed, const void* scales, int format, int scale_layout, int64_t rows, int heads,
+                     void* out, cudaStream_t st);
+int fp4_reorder_scales(const void* src, int format, int64_t mn, int64_t l_extent, int k_layout, void* dst,
+                       cudaStream_t st);
 int list_uniformity(const int32_t* work, int n_work, const int32_t* lists, int list_heads, int topk, uint8_t* flags,
                     cudaStream_t st);
 // 4-D TMA map over paged e4m3 K or V [pages, Hkv, 128, 128]: one 128x128-byte box per (page, head), 128-byte swizzle

@@ -523,3 +523,91 @@ def sampled_sparse_error(out_rows, q_rows, k_pages, v_pages, table, kv_len, firs
                                     qo_offset=[first_pos], k_scale=k_scale, v_scale=v_scale,
                                     token_chunk=token_chunk)
     return float((out_rows.float() - ref).abs().max())
+
+
+# ---------------------------------------------------------------------------
+# FP4 indexer: per-page maxima of Q K^T with Q and K as packed e2m1 + block scales
+# ---------------------------------------------------------------------------
+_E2M1 = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0])
+FP4_GROUPS = {"nvfp4": 8, "mxfp4": 4}
+
+
+def fp4_scale_to_float(scale: torch.Tensor, fmt: str) -> torch.Tensor:
+    """Block scales as float32: e4m3 (nvfp4) or ue8m0 = 2^(byte - 127) (mxfp4); raw uint8 bytes are accepted."""
+    raw = scale.view(torch.uint8).cpu().to(torch.int64)
+    if fmt == "mxfp4":
+        return torch.ldexp(torch.ones(raw.shape), (raw - 127).to(torch.int32)).float()
+    e, m = (raw >> 3) & 15, raw & 7
+    mag = torch.where(e == 0, m.double() * 2.0 ** -9, torch.ldexp(1.0 + m.double() / 8.0, (e - 7).to(torch.int32)))
+    return torch.where((raw & 0x80) != 0, -mag, mag).float()
+
+
+def fp4_dequantize(packed: torch.Tensor, scale: torch.Tensor, fmt: str) -> torch.Tensor:
+    """[..., 64] packed bytes (low nibble = even element) and logical scales [..., G] -> float32 [..., 128]; what
+    ``_decode_fp4x2_to_f32`` / ``_dequantize_public_fp4`` do in
+    python/fmha_sm100/cute/test_fp4_indexer.py:153-167."""
+    raw = packed.view(torch.uint8).cpu().to(torch.int64)
+    vals = torch.stack((_E2M1[raw & 15], _E2M1[(raw >> 4) & 15]), dim=-1).reshape(*packed.shape[:-1], 128)
+    s = fp4_scale_to_float(scale, fmt)
+    return vals * torch.repeat_interleave(s, 128 // FP4_GROUPS[fmt], dim=-1)
+
+
+def fp4_mma_scale_offset(m, g, l, mn: int, groups: int):
+    """Byte offset of scale (row m, group g, batch l) in the 128x4-tiled storage
+    (fp4_indexer_mma_scale_storage_stride, python/fmha_sm100/cute/fp4_indexer_interface.py:243-249)."""
+    rest_m, rest_g = (mn + 127) // 128, (groups + 3) // 4
+    return (l * 512 * rest_m * rest_g + (m // 128) * 512 * rest_g + (g // 4) * 512 + (m % 32) * 16
+            + ((m % 128) // 32) * 4 + g % 4)
+
+
+def fp4_reorder_scales(q_scale: torch.Tensor, k_scale: torch.Tensor, fmt: str):
+    """Logical Q [T, Hq, G] / K [P, Hk, 128, G] scale bytes -> flat uint8 storage in the 128x4-tiled layout
+    (python/fmha_sm100/cute/src/sm100/fp4_indexer.py:83-199).  Padding bytes are zero."""
+    G = FP4_GROUPS[fmt]
+    qs, ks = q_scale.view(torch.uint8).cpu(), k_scale.view(torch.uint8).cpu()
+    T, Hq, _ = qs.shape
+    P, Hk, _, _ = ks.shape
+    rest_g = (G + 3) // 4
+    q_out = torch.zeros(Hq * ((T + 127) // 128) * rest_g * 512, dtype=torch.uint8)
+    m, l, g = torch.meshgrid(torch.arange(T), torch.arange(Hq), torch.arange(G), indexing="ij")
+    q_out[fp4_mma_scale_offset(m, g, l, T, G).reshape(-1)] = qs.reshape(-1)
+    k_out = torch.zeros(P * Hk * rest_g * 512, dtype=torch.uint8)
+    l, m, g = torch.meshgrid(torch.arange(P * Hk), torch.arange(128), torch.arange(G), indexing="ij")
+    k_out[fp4_mma_scale_offset(m, g, l, 128, G).reshape(-1)] = ks.reshape(-1)
+    return q_out, k_out
+
+
+def fp4_indexer_block_scores(q_fp4, k_fp4, q_scale, k_scale, cu_seqlens_q, cu_seqlens_k, cu_page_offsets, kv_indices,
+                             fmt: str, causal: bool = False, qo_offset=None) -> torch.Tensor:
+    """``[Hq, max ceil(k_len / 128), total_q]`` float32, -inf where a page is beyond the request or wholly masked
+    (row i of a request sees key j iff ``i + offset >= j``, offset = k_len - q_len unless given): the contract of
+    ``fp4_indexer_block_scores`` as ``_reference_block_scores`` states it
+    (python/fmha_sm100/cute/test_fp4_indexer.py:273-327), one matmul per (request, head) instead of Python loops."""
+    q = fp4_dequantize(q_fp4, q_scale, fmt)
+    k = fp4_dequantize(k_fp4, k_scale, fmt)
+    cu_q, cu_k, cu_p = _as_list(cu_seqlens_q), _as_list(cu_seqlens_k), _as_list(cu_page_offsets)
+    table = kv_indices.cpu().long()
+    B = len(cu_q) - 1
+    T, Hq, _ = q.shape
+    Hk = k.shape[1]
+    hr = Hq // Hk
+    k_lens = [cu_k[b + 1] - cu_k[b] for b in range(B)]
+    max_tiles = max((kl + PAGE - 1) // PAGE for kl in k_lens) if B else 0
+    out = torch.full((Hq, max_tiles, T), NEG_INF, dtype=torch.float32)
+    for b in range(B):
+        q0, ql, kl = cu_q[b], cu_q[b + 1] - cu_q[b], k_lens[b]
+        n = (kl + PAGE - 1) // PAGE
+        if ql == 0 or n == 0:
+            continue
+        off = int(qo_offset[b]) if qo_offset is not None else kl - ql
+        pages = table[cu_p[b]:cu_p[b] + n]
+        for h in range(Hq):
+            kk = k[pages, h // hr].reshape(n * PAGE, 128)                 # [n * 128, 128]
+            s = q[q0:q0 + ql, h] @ kk.T                                   # [ql, n * 128]
+            col = torch.arange(n * PAGE).view(1, -1)
+            vis = col < kl
+            if causal:
+                vis = vis & (torch.arange(ql).view(-1, 1) + off >= col)
+            s = torch.where(vis, s, torch.full_like(s, NEG_INF))
+            out[h, :n, q0:q0 + ql] = s.view(ql, n, PAGE).amax(dim=2).T
+    return out

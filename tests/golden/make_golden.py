@@ -11,6 +11,8 @@ It imports, unmodified, the reference oracles
   python/fmha_sm100/cute/test_sparse_atten.py  sparse_attention_ref
   python/fmha_sm100/cute/sparse_index_utils.py build_k2q_csr_torch_reference
   python/fmha_sm100/cute/quantize.py     dequantize_nvfp4_128x4_to_bf16
+  python/fmha_sm100/cute/test_fp4_indexer.py       _reference_block_scores, _dequantize_public_fp4
+  python/fmha_sm100/cute/fp4_indexer_interface.py  fp4_indexer_mma_scale_shape / _stride
 runs them on small seeded inputs and stores inputs + outputs as .npz files
 next to this script.  tests/test_oracle_golden.py replays the stored inputs
 through oracle/msa_oracle.py and compares.  The reference tree is needed only
@@ -148,6 +150,46 @@ def main(ref_root):
     offs = rq.nvfp4_scale_128x4_offset(r, c, 8)
     np.savez_compressed(os.path.join(HERE, "nvfp4.npz"), x=_np(x), data=data.numpy(), scale=sflat.numpy(), gs=gs,
                         deq_bf16=_np(deq), offsets=offs.numpy())
+    # ---- 8. FP4 indexer: the reference's own CPU scorer and scale-storage strides on seeded random inputs
+    import fp4_indexer_interface as fii
+    import test_fp4_indexer as tfi
+    out = {}
+    for fmt in ("nvfp4", "mxfp4"):
+        g = torch.Generator().manual_seed(16)
+        ql, kl, hq, hk = [70, 130], [300, 200], 4, 2
+        groups = fii.normalize_fp4_format(fmt).scale_groups
+        pages = [(x + 127) // 128 for x in kl]
+        n_pages = sum(pages) + 1
+        q = torch.randint(0, 256, (sum(ql), hq, 64), dtype=torch.uint8, generator=g)
+        k = torch.randint(0, 256, (n_pages, hk, 128, 64), dtype=torch.uint8, generator=g)
+        qs = tfi._random_scale((sum(ql), hq, groups), fmt=fmt, device=torch.device("cpu"), generator=g)
+        ks = tfi._random_scale((n_pages, hk, 128, groups), fmt=fmt, device=torch.device("cpu"), generator=g)
+        cu_q = torch.tensor([0, 70, 200], dtype=torch.int32)
+        cu_k = torch.tensor([0, 300, 500], dtype=torch.int32)
+        cu_p = torch.tensor([0, 3, 5], dtype=torch.int32)
+        kvi = torch.randperm(n_pages, generator=g)[:5].to(torch.int32)
+        off = torch.tensor([100, 60], dtype=torch.int32)
+        out.update({f"{fmt}_q": q.numpy(), f"{fmt}_k": k.numpy(), f"{fmt}_qs": qs.view(torch.uint8).numpy(),
+                    f"{fmt}_ks": ks.view(torch.uint8).numpy(), f"{fmt}_kvi": kvi.numpy()})
+        for name, causal, o in (("dense", False, None), ("causal", True, None), ("offset", True, off)):
+            out[f"{fmt}_{name}"] = tfi._reference_block_scores(q, k, qs, ks, cu_q, cu_k, cu_p, fmt=fmt, kv_indices=kvi,
+                                                               causal=causal, qo_offset=o).numpy()
+        out[f"{fmt}_deq_q"] = tfi._dequantize_public_fp4(q, qs, fmt=fmt).numpy()
+        # the tiled scale storage, built from the reference's own shape / stride helpers
+        for tag, src, mn, l in (("qs", qs.view(torch.uint8), sum(ql), hq),
+                                ("ks", ks.view(torch.uint8).reshape(n_pages * hk, 128, groups).permute(1, 0, 2), 128,
+                                 n_pages * hk)):
+            shape = fii.fp4_indexer_mma_scale_shape(mn, l, fp4_format=fmt)
+            stride = fii.fp4_indexer_mma_scale_stride(mn, l, fp4_format=fmt)
+            nbytes = math.prod(fii.fp4_indexer_mma_scale_storage_shape(mn, l, fp4_format=fmt))
+            flat = torch.zeros(nbytes, dtype=torch.uint8)
+            view = torch.as_strided(flat, shape, stride)      # (32, 4, restM, 4, restG, L)
+            for m in range(mn):
+                for gi in range(groups):
+                    view[m % 32, (m // 32) % 4, m // 128, gi % 4, gi // 4, :] = src[m, :, gi]
+            out[f"{fmt}_{tag}_mma"] = flat.numpy()
+    np.savez_compressed(os.path.join(HERE, "fp4_indexer.npz"), cu_q=cu_q.numpy(), cu_k=cu_k.numpy(), cu_p=cu_p.numpy(),
+                        off=off.numpy(), **out)
     print("golden fixtures written to", HERE)
 
 

@@ -3,6 +3,7 @@
 import os
 
 import numpy as np
+import pytest
 import torch
 
 from oracle import msa_oracle as O
@@ -204,3 +205,25 @@ def test_kv_append_oracle_matches_whole_tensor_quantisers():
     off = (k8 != want)
     assert off.float().mean() < 1e-3 and (k8.int() - want.int()).abs().max() <= 1     # reciprocal vs division
     assert torch.equal(k8[skipped // 128, :, skipped % 128], want[skipped // 128, :, skipped % 128])
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4"])
+def test_fp4_indexer_fixture(fmt):
+    """FP4 indexer oracle against the reference's own CPU scorer, dequantiser and scale-storage strides
+    (python/fmha_sm100/cute/test_fp4_indexer.py:153-327, fp4_indexer_interface.py:220-249)."""
+    z = np.load(os.path.join(G, "fp4_indexer.npz"))
+    q, k = torch.from_numpy(z[f"{fmt}_q"]), torch.from_numpy(z[f"{fmt}_k"])
+    qs, ks = torch.from_numpy(z[f"{fmt}_qs"]), torch.from_numpy(z[f"{fmt}_ks"])
+    cu_q, cu_k, cu_p = (torch.from_numpy(z[n]) for n in ("cu_q", "cu_k", "cu_p"))
+    kvi, off = torch.from_numpy(z[f"{fmt}_kvi"]), torch.from_numpy(z["off"])
+    assert torch.equal(O.fp4_dequantize(q, qs, fmt), torch.from_numpy(z[f"{fmt}_deq_q"]))
+    for name, causal, o in (("dense", False, None), ("causal", True, None), ("offset", True, off)):
+        ref = torch.from_numpy(z[f"{fmt}_{name}"])
+        got = O.fp4_indexer_block_scores(q, k, qs, ks, cu_q, cu_k, cu_p, kvi, fmt, causal=causal, qo_offset=o)
+        assert got.shape == ref.shape
+        fin = torch.isfinite(ref)
+        assert torch.equal(fin, torch.isfinite(got))
+        assert torch.allclose(got[fin], ref[fin], rtol=2e-6, atol=1e-3)      # float32 summation order only
+    q_mma, k_mma = O.fp4_reorder_scales(qs, ks, fmt)
+    assert torch.equal(q_mma, torch.from_numpy(z[f"{fmt}_qs_mma"]))
+    assert torch.equal(k_mma, torch.from_numpy(z[f"{fmt}_ks_mma"]))
