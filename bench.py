@@ -28,6 +28,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
 SEQ_LENS = (16384, 32768, 65536, 131072)
@@ -416,6 +417,73 @@ def reference_sm100_stage(dev, lens, which="fp8", hq=HQ, hkv=HKV, topk=TOPK, ite
     return res
 
 
+FP4_CASES = {   # shapes of the reference's published FP4 indexer table (python/fmha_sm100/cute/README.md:396-411)
+    "prefill_q8k_k8k": dict(q_lens=[8192], k_lens=[8192]),
+    "prefill_q8k_k64k": dict(q_lens=[8192], k_lens=[65536]),
+    "decode_uniform": dict(q_lens=[8] * 30, k_lens=[67584] * 30),
+}
+
+
+def fp4_indexer_stage(dev, fmt, case, with_reference, hq=64, hkv=4, iters=5):
+    """fp4_indexer_block_scores on one case of the reference's own benchmark (random packed bytes, scale bytes from
+    its test's range, shuffled pages, causal, preordered scales; effective FLOPs = visible (query, key) pairs x 256
+    x Hq, the convention of _causal_effective_score_flops in python/fmha_sm100/cute/test_fp4_indexer.py:684-698),
+    and, when the reference is installed under baseline/_ref, the reference's kernel on the same tensors."""
+    import msa_b200
+    q_lens, k_lens = FP4_CASES[case]["q_lens"], FP4_CASES[case]["k_lens"]
+    g = torch.Generator(device=dev).manual_seed(21)
+    groups = 8 if fmt == "nvfp4" else 4
+    lo, hi = (16, 89) if fmt == "nvfp4" else (122, 133)
+    sdt = torch.float8_e4m3fn if fmt == "nvfp4" else torch.float8_e8m0fnu
+    pages = [(k + PAGE - 1) // PAGE for k in k_lens]
+    T, P = sum(q_lens), sum(pages)
+    q = torch.randint(0, 256, (T, hq, 64), dtype=torch.uint8, device=dev, generator=g)
+    k = torch.randint(0, 256, (P, hkv, PAGE, 64), dtype=torch.uint8, device=dev, generator=g)
+    qs = torch.randint(lo, hi, (T, hq, groups), dtype=torch.uint8, device=dev, generator=g).view(sdt)
+    ks = torch.randint(lo, hi, (P, hkv, PAGE, groups), dtype=torch.uint8, device=dev, generator=g).view(sdt)
+    cu = lambda v: torch.tensor([0] + list(np.cumsum(v)), dtype=torch.int32, device=dev)  # noqa: E731
+    cu_q, cu_k, cu_p = cu(q_lens), cu(k_lens), cu(pages)
+    kvi = torch.randperm(P, device=dev, generator=g).int()
+    q_mma, k_mma = msa_b200.fp4_indexer_reorder_scales_for_mma_cute(qs, ks, fp4_format=fmt)
+    # the contiguous storage behind the views: what the reference's validator wants to see
+    q_st, k_st = q_mma.permute(5, 2, 4, 0, 1, 3), k_mma.permute(5, 2, 4, 0, 1, 3)
+    kw = dict(max_seqlen_q=max(q_lens), max_seqlen_k=max(k_lens), kv_indices=kvi, fp4_format=fmt, causal=True,
+              scale_layout="preordered_mma")
+    ours = lambda: msa_b200.fp4_indexer_block_scores(q, k, q_st, k_st, cu_q, cu_k, cu_p, **kw)  # noqa: E731
+    vis = sum(sum(max(0, min(kl, i + kl - ql + 1)) for i in range(ql)) for ql, kl in zip(q_lens, k_lens))
+    flops = 2.0 * hq * vis * 128
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    mo, _ = time_fn(ours, iters, 2, flush=flush)
+    res = {"case": case, "format": fmt, "num_qo_heads": hq, "num_kv_heads": hkv,
+           "ours": {"ms": mo, "tflops_effective": flops / (mo * 1e-3) / 1e12,
+                    "what": "dequantise Q, -inf fill, score kernel with fused K dequantisation"}}
+    if with_reference:
+        try:
+            ref_root = os.path.join(ROOT, "baseline", "_ref")
+            cute = os.path.join(ref_root, "fmha_sm100", "cute")
+            os.environ.setdefault("MM_SPARSE_ATTN_AOT_CACHE", os.path.join(ref_root, "aot_cache"))
+            for pth in (ref_root, cute):
+                if pth not in sys.path:
+                    sys.path.insert(0, pth)
+            import fp4_indexer_interface as rfi       # the reference module, unmodified
+            theirs = lambda: rfi.fp4_indexer_block_scores(q, k, q_st, k_st, cu_q, cu_k, cu_p, **kw)  # noqa: E731
+            t0 = time.perf_counter()
+            out_r = theirs()
+            torch.cuda.synchronize()
+            res["reference_first_call_s"] = round(time.perf_counter() - t0, 1)
+            mr, _ = time_fn(theirs, iters, 2, flush=flush)
+            res["reference"] = {"ms": mr, "tflops_effective": flops / (mr * 1e-3) / 1e12}
+            res["speedup_vs_reference"] = mr / mo
+            out_o = ours()
+            fin = torch.isfinite(out_r)
+            res["finite_pattern_equal"] = bool(torch.equal(fin, torch.isfinite(out_o)))
+            res["max_rel_diff_vs_reference"] = float(((out_o[fin] - out_r[fin]).abs() /
+                                                      out_r[fin].abs().clamp_min(1.0)).max())
+        except Exception as e:  # the reference failed to import, compile or launch on this box
+            res["reference"] = {"unavailable": f"{type(e).__name__}: {str(e).splitlines()[0] if str(e) else ''}"[:300]}
+    return res
+
+
 def sampled_output_check(w, samples_per_request=1):
     """Max-abs difference between the timed launch's output and the CPU oracle on the last 128-query block of
     every request plus a middle block of the longest one, all heads (outside the timed region)."""
@@ -638,8 +706,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="skip stages / decode / e2e (profiling runs)")
-    ap.add_argument("--stage", default="prefill", choices=["prefill", "decode", "topk", "proxy", "kvappend", "reference_sm100"],
+    ap.add_argument("--stage", default="prefill", choices=["prefill", "decode", "topk", "proxy", "kvappend", "reference_sm100", "fp4_indexer"],
                     help="profiling runs: time only this stage and print a short JSON line")
+    ap.add_argument("--no-ref", action="store_true", help="--stage fp4_indexer: skip the reference's kernel")
     ap.add_argument("--ref-kv", default="both", choices=["both", "fp8", "nvfp4"],
                     help="--stage reference_sm100: which K/V format to run")
     ap.add_argument("--decode-batch", type=int, default=32, help="requests of the decode case (131072-token contexts)")
@@ -700,6 +769,17 @@ def main():
                 out[which] = reference_sm100_stage(dev, which=which, **kw)
             except Exception as e:  # the reference failed to import, compile or launch on this box
                 out[which] = {"unavailable": f"{type(e).__name__}: {str(e).splitlines()[0] if str(e) else ''}"[:300]}
+        print(json.dumps(out), flush=True)
+        return
+    if args.stage == "fp4_indexer":
+        have_ref = os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "fmha_sm100", "cute"))
+        out = {"stage": "fp4_indexer", "cases": []}
+        for case in FP4_CASES:
+            for fmt in ("nvfp4", "mxfp4"):
+                try:
+                    out["cases"].append(fp4_indexer_stage(dev, fmt, case, have_ref and not args.no_ref))
+                except Exception as e:  # noqa: BLE001
+                    out["cases"].append({"case": case, "format": fmt, "error": f"{type(e).__name__}: {e}"[:300]})
         print(json.dumps(out), flush=True)
         return
     if args.stage == "proxy":

@@ -13,11 +13,11 @@
 //   warp 8     producer: Q tiles of the item (of the NEXT item into the other buffer where shared memory allows
 //              two), K pages two at a time into a ring of page PAIRS (the two pages of a pair lie back to back,
 //              so they form one 256-row operand)
-//   warps 9,10 MMA issuers, one per tile: one tcgen05.mma per k-step with N = 256 covers both pages of a pair (half
-//              the instructions, commits and barrier polls per page of N = 128); tile t accumulates into TMEM
-//              columns [256 t, 256 t + 256); tcgen05.commit hands S to the row-max group, and -- one arrival per
-//              issuer -- releases the K pair and, after the item's last pair, the Q buffer.  (With packed e2m1 K
-//              warps 10-11 dequantise, and warp 9 issues for both tiles.)
+//   warps 9,10 MMA issuers, one per tile (one thread spends about as long polling barriers and committing as
+//              issuing, so with two the pipe stays fed): tile t accumulates page e of a pair into TMEM columns
+//              [256 t + 128 e, + 128); tcgen05.commit hands each page's S to the row-max group, and -- one
+//              arrival per issuer -- releases the K pair and, after the item's last pair, the Q buffer
+//   warps 11-15 (packed e2m1 K only; the CTA then has 16 warps) dequantise raw pages into f16 operand tiles
 //   warps 0-3  row-max group of tile 0: thread = query row; S in 64-column chunks, two in flight; the buffer goes
 //   warps 4-7  back as soon as the last chunk has landed.  Same for tile 1.  While one tile's S is being read the
 //              tensor pipe works on the other tile.
@@ -48,14 +48,20 @@ struct ScoreCfg {
   static constexpr int kRingBytes = kKDirectFp8 ? kPairsHalf * kPairBytes / 2 : kPairs * kPairBytes;
   static constexpr int kRawStages = kKConvert ? 3 : 0;
   static constexpr int kRawBytes = 8192 + 1024;                              // packed e2m1 page + its scales
-  static constexpr int kThreads = 384;
-  static constexpr int kProducerWarp = 8, kMmaWarp = 9, kCvtWarp0 = 10;
+  // 12 warps; 16 with packed e2m1 K, where warps 11-15 dequantise (two warps kept the tensor pipe 40 % busy)
+  static constexpr int kThreads = kKConvert ? 512 : 384;
+  static constexpr int kProducerWarp = 8, kMmaWarp = 9, kMmaWarp1 = 10, kCvtWarp0 = 11;
+  static constexpr int kCvtWarps = kKConvert ? 5 : 0;
   // One thread spends about as long polling barriers and committing as issuing; with an issuer per tile one of
-  // them is always feeding the pipe.  Warp 10 converts K in the e2m1 mode, which keeps a single issuer.
-  static constexpr int kIssuers = kKConvert ? 1 : 2;
-  // 256 row-max threads at 216 registers + 128 helper threads at 72 = 384 x 168 (see FmhaCfg)
-  static constexpr int kRegsLaunch = 168, kRegsRowMax = 216, kRegsHelper = 72;
-  static_assert(256 * kRegsRowMax + 128 * kRegsHelper == 384 * kRegsLaunch, "setmaxnreg budget must balance");
+  // them is always feeding the pipe.
+  static constexpr int kIssuers = 2;
+  // setmaxnreg.inc waits, unbounded, for registers released inside the CTA's own launch allocation, so the totals
+  // must balance exactly: 256 row-max threads + the helper threads = threads x launch count
+  static constexpr int kRegsLaunch = kKConvert ? 128 : 168;
+  static constexpr int kRegsRowMax = kKConvert ? 176 : 216;
+  static constexpr int kRegsHelper = kKConvert ? 80 : 72;
+  static_assert(256 * kRegsRowMax + (kThreads - 256) * kRegsHelper == kThreads * kRegsLaunch,
+                "setmaxnreg budget must balance");
   static constexpr int kFmt16 = kQuant ? 0 : 1;   // f16 once K is dequantised, bf16 as loaded
 };
 
@@ -147,7 +153,7 @@ __device__ __forceinline__ void issue_score_qk(uint32_t q_saddr, uint32_t k_sadd
 }
 
 template <int KVMODE>
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(ScoreCfg<KVMODE>::kThreads, 1)
 score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const FmhaParams p) {
   using Cfg = ScoreCfg<KVMODE>;
@@ -176,12 +182,12 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       }
     }
     for (int s = 0; s < Cfg::kMaxPairs; ++s) {
-      mbar_init(&sm.k_full[s], Cfg::kKConvert ? 2 : 1);
+      mbar_init(&sm.k_full[s], Cfg::kKConvert ? Cfg::kCvtWarps : 1);
       mbar_init(&sm.k_empty[s], Cfg::kIssuers);
     }
     for (int s = 0; s < NRAW; ++s) {
       mbar_init(&sm.raw_full[s], 1);
-      mbar_init(&sm.raw_empty[s], 2);
+      mbar_init(&sm.raw_empty[s], Cfg::kKConvert ? Cfg::kCvtWarps : 1);
     }
     sm.abort = 0;
     mbar_fence_init();
@@ -504,7 +510,7 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
         MSA_TFLUSH(true, 12, 14)
       }
-    } else if (warp == Cfg::kMmaWarp || (Cfg::kIssuers == 2 && warp == Cfg::kCvtWarp0)) {
+    } else if (warp == Cfg::kMmaWarp || warp == Cfg::kMmaWarp1) {
       // =======================================================================
       // MMA issuer: tile `me` with two issuers, both tiles with one.  tcgen05.commit covers the MMAs of the
       // committing thread only, hence K pairs and Q buffers are released by one arrival per issuer.
@@ -569,14 +575,13 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       MSA_TFLUSH(lane == 0 && me == 0, 14, 15)
     } else if constexpr (Cfg::kKConvert) {
       // =======================================================================
-      // dequantise raw e2m1 pages into f16 operand tiles (64 threads; a thread owns one 16-value block of every
-      // 8th row).  Block scales: e4m3 per 16 values (two 128x4 tiles per page) or, with k_mx, ue8m0 per 32 (one).
+      // dequantise raw e2m1 pages into f16 operand tiles (warps 11-15).  Block scales: e4m3 per 16 values (two
+      // 128x4 tiles per page) or, with k_mx, ue8m0 per 32 (one).
       // =======================================================================
-      const int ct = tid - Cfg::kCvtWarp0 * 32;  // 0..63
-      const int r8 = ct >> 3, c8 = ct & 7;
-      const uint32_t sw0 = (((c8 & 3) * 2) ^ r8) << 4, sw1 = (((c8 & 3) * 2 + 1) ^ r8) << 4;
+      const int cw = warp - Cfg::kCvtWarp0;      // convert warp 0 .. kCvtWarps - 1
+      const int r4 = lane >> 3, c8 = lane & 7;   // row within a group of 4, 16-value block of the row
       const bool mx = p.k_mx != 0;
-      bool ok = true;
+      bool ok = cw < Cfg::kCvtWarps;
       uint32_t raw_seq = 0, pair_seq = 0;
       int j = 0;
       ScoreItem it;
@@ -591,15 +596,17 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             ok = mbar_wait(&sm.raw_full[rs], (raw_seq / NRAW) & 1, abort_flag);
             if (!ok) break;
             const uint8_t* rawp = sm.raw[rs];
-            uint8_t* dst = sm.k + kq * pair_bytes + e * kHalfBytes + (c8 >> 2) * kTileBytes + r8 * 128;
-            const uint8_t* src = rawp + ct * 8;
-            // scale of (row, block): 128x4 tile offset (row % 32) * 16 + (row / 32) * 4 + block % 4; with ue8m0
-            // scales a block of 16 values shares the scale of its group of 32 (block c8 -> group c8 / 2)
-            const uint8_t* sc = mx ? rawp + 8192 + r8 * 16 + (c8 >> 1) : rawp + 8192 + (c8 >> 2) * 512 + r8 * 16 + (c8 & 3);
-#pragma unroll 4
-            for (int i = 0; i < 16; ++i) {
-              const uint2 x = *reinterpret_cast<const uint2*>(src + i * 512);
-              const uint32_t sb = sc[(i & 3) * 128 + (i >> 2) * 4];
+            uint8_t* tile = sm.k + kq * pair_bytes + e * kHalfBytes + (c8 >> 2) * kTileBytes;
+            // a warp takes every kCvtWarps-th group of four rows; block c8 of row `row`: 8 packed bytes in, two
+            // 16-byte chunks of the 128-byte swizzled f16 row out.  Scale of (row, block): 128x4 tile offset
+            // (row % 32) * 16 + (row / 32) * 4 + block % 4; with ue8m0 scales a block of 16 values shares the
+            // scale of its group of 32 (block c8 -> group c8 / 2)
+            const uint8_t* sc = mx ? rawp + 8192 + (c8 >> 1) : rawp + 8192 + (c8 >> 2) * 512 + (c8 & 3);
+#pragma unroll 2
+            for (int i = cw; i < 32; i += Cfg::kCvtWarps) {
+              const int row = i * 4 + r4, r8 = row & 7;
+              const uint2 x = *reinterpret_cast<const uint2*>(rawp + row * 64 + c8 * 8);
+              const uint32_t sb = sc[(row & 31) * 16 + (row >> 5) * 4];
               uint32_t s2;
               if (mx) {
                 // 2^(e - 127) as f16, exact for exponents -24 .. 15 (clamped outside)
@@ -622,8 +629,9 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
               b.y = hmul2_u32(f1[1], s2);
               b.z = hmul2_u32(f1[2], s2);
               b.w = hmul2_u32(f1[3], s2);
-              *reinterpret_cast<uint4*>(dst + i * 1024 + sw0) = a;
-              *reinterpret_cast<uint4*>(dst + i * 1024 + sw1) = b;
+              uint8_t* dst = tile + row * 128;
+              *reinterpret_cast<uint4*>(dst + ((((c8 & 3) * 2) ^ r8) << 4)) = a;
+              *reinterpret_cast<uint4*>(dst + ((((c8 & 3) * 2 + 1) ^ r8) << 4)) = b;
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.raw_empty[rs]);
