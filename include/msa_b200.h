@@ -68,8 +68,9 @@ typedef struct msa_plan_desc {
   int32_t kv_block_num;     /* page-list length of a sparse call (> 0), else <= 0 */
   int32_t num_kv_splits;    /* > 0 forces the decode split count, else chosen for whole waves of CTAs */
   int32_t num_sms;          /* SMs the decode split choice may assume (usable_SM_count), <= 0 = 148 */
-  int32_t tile_rows;        /* query rows per work entry: 0 or 128; 256 for the score-only pass, whose work items
-                               are two query tiles against one stream of K pages (msa_fmha_args.tile_rows) */
+  int32_t tile_rows;        /* query tokens per work entry: 0 or 128; 256 for the score-only pass, whose work items
+                               are two query tiles against one stream of K pages (msa_fmha_args.tile_rows); any
+                               value up to 256 (256 / hb with msa_fmha_args.score_pack_heads = hb) */
   int32_t dense_kv_splits;  /* > 1: every query tile becomes this many work entries, each over a contiguous range of
                                the tile's visible pages, writing output rows split * total_q + token (merged by
                                msa_fmha_combine); for dense calls whose query tiles alone cannot fill the GPU.
@@ -192,7 +193,12 @@ typedef struct msa_fmha_args {
                                     e4m3 scale per 16 values (1024 scale bytes per (page, head), two 128x4 tiles),
                                     1 = one ue8m0 scale per 32 values (MXFP4: 512 bytes, one 128x4 tile; exponents
                                     outside 2^-24 .. 2^15 saturate) */
-  int32_t reserved0;
+  int32_t score_pack_heads;      /* score-only pass: 0 or 1 = one query head per 128-row tile; hb > 1 (a power of two
+                                    dividing the query heads per KV head) = a tile holds 128 / hb tokens x hb heads,
+                                    for requests that bring only a few tokens (decode): `work` then holds entries of up
+                                    to 256 / hb tokens (msa_plan_desc.tile_rows = 256 / hb = msa_fmha_args.tile_rows).
+                                    An entry may also cover only the pages from `first page` up (work[2] >> 10, as
+                                    msa_plan_desc.dense_kv_splits writes it): per-page maxima need no merging */
   int64_t out_rows;              /* rows of out / lse; 0 = total_q.  dense_kv_splits * total_q when the work list
                                     was planned with KV splits: out and lse are then the partial buffers that
                                     msa_fmha_combine merges (lse must be given) */

@@ -53,10 +53,11 @@ static int make_o_map(CUtensorMap* m, const void* o, int64_t total_q, int hq) {
   return make_map(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, o, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
 }
 
-static int make_q_map(CUtensorMap* m, const void* q, int64_t total_q, int hq) {
+// pack_heads = hb > 1 (score-only pass over short requests): a tile is 128 / hb tokens x hb adjacent heads
+static int make_q_map(CUtensorMap* m, const void* q, int64_t total_q, int hq, int pack_heads = 1) {
   const uint64_t dims[3] = {128, static_cast<uint64_t>(hq), static_cast<uint64_t>(total_q)};
   const uint64_t strides[2] = {256, static_cast<uint64_t>(hq) * 256};
-  const uint32_t box[3] = {64, 1, 128};
+  const uint32_t box[3] = {64, static_cast<uint32_t>(pack_heads), static_cast<uint32_t>(128 / pack_heads)};
   return make_map(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, q, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
@@ -183,8 +184,14 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
   if (score_only && sparse) return MSA_ERR_UNSUPPORTED;        // the pass over page lists has no max-score output
   if (a->k_scale_format != 0 && (a->k_scale_format != 1 || !score_only || a->kv_dtype != MSA_KV_NVFP4))
     return MSA_ERR_INVALID;
-  if (a->tile_rows != 0 && a->tile_rows != 128 && a->tile_rows != 256) return MSA_ERR_INVALID;
-  if (a->tile_rows == 256 && !score_only) return MSA_ERR_UNSUPPORTED;
+  // heads per query tile of the score-only pass: a power of two that divides the heads per KV head; a work entry
+  // then covers up to 256 / hb tokens
+  const int hb = a->score_pack_heads > 1 ? a->score_pack_heads : 1;
+  if (hb > 1 && (!score_only || (hb & (hb - 1)) != 0 || hb > 128 ||
+                 (a->num_qo_heads / a->num_kv_heads) % hb != 0 || a->tile_rows != 256 / hb))
+    return MSA_ERR_INVALID;
+  if (hb == 1 && a->tile_rows != 0 && a->tile_rows != 128 && a->tile_rows != 256) return MSA_ERR_INVALID;
+  if (hb == 1 && a->tile_rows == 256 && !score_only) return MSA_ERR_UNSUPPORTED;
   if (a->n_work <= 0 || a->total_q <= 0) return MSA_OK;
   const int64_t out_rows = a->out_rows > 0 ? a->out_rows : a->total_q;
 
@@ -225,7 +232,8 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
 
   // two query heads share one K/V stream when they share a KV head and a page list
   int nt = (p.hr % 2 == 0 && (!sparse || a->list_heads == a->num_kv_heads)) ? 2 : 1;
-  if (score_only) nt = 1;   // the score kernel takes one head per work item
+  if (score_only) nt = hb;  // the score kernel takes hb heads per work item
+  p.pack_heads = hb;
   p.pair_tiles = 0;
   p.n_head_groups = p.Hq / nt;
   const long long n_items = static_cast<long long>(p.n_work) * p.n_head_groups;
@@ -233,7 +241,7 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
   p.n_items = static_cast<int>(n_items);
 
   CUtensorMap mq, mk, mv, mo;
-  int rc = make_q_map(&mq, a->q, a->total_q, p.Hq);
+  int rc = make_q_map(&mq, a->q, a->total_q, p.Hq, score_only ? hb : 1);
   if (rc != MSA_OK) return rc;
   // score-only calls have no output: the map is never used then, but must be a valid one
   rc = make_o_map(&mo, a->out != nullptr ? a->out : a->q, a->out != nullptr ? out_rows : a->total_q, p.Hq);

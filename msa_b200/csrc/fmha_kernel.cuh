@@ -77,6 +77,7 @@ struct FmhaParams {
   int k_scale_tile_bytes;        // score-only pass over packed e2m1 K: scale bytes per (page, head): 1024 (e4m3 per 16
                                  // values) or 512 (ue8m0 per 32 values, k_mx)
   int k_mx;
+  int pack_heads;                // score-only pass: query heads per 128-row tile (a power of two dividing hr), else 1
   const uint8_t* k_raw;          // NVFP4 raw page storage
   const uint8_t* v_raw;
   int Hq, Hkv, hr, topk, list_heads, total_q, max_k_tiles, n_work, n_head_groups, n_items;

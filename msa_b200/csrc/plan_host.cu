@@ -17,15 +17,14 @@ constexpr int kPage = 128;
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
-inline int tile_rows_of(const msa_plan_desc* d) { return d->tile_rows == 256 ? 256 : kPage; }
+inline int tile_rows_of(const msa_plan_desc* d) { return d->tile_rows > 0 ? d->tile_rows : kPage; }
 
 inline int kv_splits_of(const msa_plan_desc* d) { return d->dense_kv_splits > 1 ? d->dense_kv_splits : 1; }
 
 int plan_check(const msa_plan_desc* d) {
   if (d == nullptr || d->batch < 0) return MSA_ERR_INVALID;
-  if (d->tile_rows != 0 && d->tile_rows != 128 && d->tile_rows != 256) return MSA_ERR_INVALID;
-  if (d->dense_kv_splits < 0 || d->dense_kv_splits > 1024 || (d->dense_kv_splits > 1 && d->tile_rows == 256))
-    return MSA_ERR_INVALID;
+  if (d->tile_rows < 0 || d->tile_rows > 256) return MSA_ERR_INVALID;
+  if (d->dense_kv_splits < 0 || d->dense_kv_splits > 1024) return MSA_ERR_INVALID;
   if (d->batch > 0 && (d->qo_lens == nullptr || d->kv_lens == nullptr)) return MSA_ERR_INVALID;
   if (d->num_qo_heads <= 0 || d->num_kv_heads <= 0 || d->num_qo_heads % d->num_kv_heads != 0) return MSA_ERR_INVALID;
   for (int b = 0; b < d->batch; ++b)

@@ -85,27 +85,34 @@ constexpr int score_smem_bytes() {
   return static_cast<int>(sizeof(ScoreSmem<KVMODE>)) + 1024;
 }
 
-// Up to 256 query rows of one head: tile 0 = rows [0, 128), tile 1 = rows [128, 256) of the work entry.
+// Two query tiles of 128 rows that share one stream of K pages.  A tile holds 128 / hb consecutive tokens of hb
+// query heads of one KV head (hb = FmhaParams::pack_heads; row r = token r / hb, head r % hb): hb = 1 for prefill,
+// hb > 1 packs the heads of a GQA group into the tile when a request brings only a few tokens (decode).  The walk
+// covers the pages [page_lo, n_pages) from the top down; page_lo > 0 when the planner split the page range of an
+// entry over several work items (the per-page maxima of different pages are independent, so nothing is merged).
 struct ScoreItem {
-  int tok0, rows, qloc0, h, g, kv_len, qo_off, kv_base, n_pages, n_tiles;
+  int tok0, tokens, qloc0, h, g, kv_len, qo_off, kv_base, n_pages, n_walk, n_tiles;
 };
 
 __device__ __forceinline__ ScoreItem score_item(const FmhaParams& p, int item) {
   ScoreItem it;
-  const int wi = item / p.Hq;
-  it.h = item - wi * p.Hq;   // head fastest: CTAs running side by side share K pages
+  const int n_hg = p.Hq / p.pack_heads;
+  const int wi = item / n_hg;
+  it.h = (item - wi * n_hg) * p.pack_heads;   // first head; head group fastest: CTAs side by side share K pages
   it.g = it.h / p.hr;
   const int4 w = __ldg(p.work + 2 * wi), w2 = __ldg(p.work + 2 * wi + 1);
   it.tok0 = w.y;
-  it.rows = w.z;
+  it.tokens = w.z & 1023;
+  const int page_lo = w.z >> 10;
   it.qloc0 = w.w;
   it.kv_len = w2.x;
   it.qo_off = w2.y;
   it.kv_base = w2.z;
-  it.n_tiles = it.rows > 128 ? 2 : 1;
-  int vis = it.kv_len;   // keys visible to the last row of the entry
-  if (p.causal) vis = min(vis, it.qloc0 + it.rows + it.qo_off);
+  it.n_tiles = it.tokens * p.pack_heads > 128 ? 2 : 1;
+  int vis = it.kv_len;   // keys visible to the last token of the entry
+  if (p.causal) vis = min(vis, it.qloc0 + it.tokens + it.qo_off);
   it.n_pages = vis > 0 ? (vis + 127) >> 7 : 0;
+  it.n_walk = max(0, it.n_pages - page_lo);
   return it;
 }
 
@@ -222,10 +229,11 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         continue;   // a hole in the last (partial) round
       }
       it = score_item(p, item);
-      if (it.n_pages > 0) return true;
+      if (it.n_walk > 0) return true;
     }
   };
   // e4m3 K over the first 64 head-dim elements only: the TMA box is 64 bytes wide, a page takes 8 KiB
+  const int pack_shift = 31 - __clz(p.pack_heads);   // pack_heads is a power of two
   const bool fp8_half = Cfg::kKDirectFp8 && p.half_dim != 0;
   const uint32_t page_stride = fp8_half ? kHalfBytes / 2 : kHalfBytes;   // second page: rows 128-255 of the operand
   const int NP = fp8_half ? Cfg::kPairsHalf : Cfg::kPairs;               // pairs in the K ring
@@ -330,21 +338,23 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       j_next = j + 1;
       const bool have_next = next_item(j_next, it_next);
       if (QB == 1) convert_q(n_q, it.n_tiles);   // a single Q buffer: rewritten when the item starts
-      const int r_tile = t * 128 + r;            // my row within the work entry
-      const bool row_valid = r_tile < it.rows;
+      const int r_entry = t * 128 + r;                       // my row within the work entry
+      const int tok_local = r_entry >> pack_shift;           // its token and head
+      const int head = it.h + (r_entry & (p.pack_heads - 1));
+      const bool row_valid = tok_local < it.tokens;
       int limit_base = -1;
       if (row_valid) {
         limit_base = it.kv_len - 1;
-        if (p.causal) limit_base = min(limit_base, it.qloc0 + r_tile + it.qo_off);
+        if (p.causal) limit_base = min(limit_base, it.qloc0 + tok_local + it.qo_off);
       }
       float row_scale = 1.0f;
-      float* dst = p.max_score + static_cast<long long>(it.h) * p.ms_head + it.tok0 + r_tile;
-      const int n = it.n_pages, n_pairs = (n + 1) >> 1;
+      float* dst = p.max_score + static_cast<long long>(head) * p.ms_head + it.tok0 + tok_local;
+      const int n = it.n_pages, n_pairs = (it.n_walk + 1) >> 1;
       const bool mine = t < it.n_tiles;
       for (int pi = 0; pi < n_pairs && ok; ++pi) {
         if (mine) {
           const int page_a = n - 1 - 2 * pi, page_b = page_a - 1;   // pages are walked from the highest down
-          const bool two = page_b >= 0;
+          const bool two = 2 * pi + 1 < it.n_walk;
           MSA_TBEGIN
           ok = mbar_wait(&sm.sc_full[t][0], use_a & 1, abort_flag);
           MSA_TEND(0)
@@ -442,8 +452,9 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           ++n_q;
           mbar_expect_tx(&sm.q_full[qb], qi.n_tiles * kTileBytes);
           for (int t = 0; t < qi.n_tiles; ++t) {
-            tma_load_3d(sm.q[qb][t], &tmap_q, &sm.q_full[qb], 0, qi.h, qi.tok0 + t * 128);
-            tma_load_3d(sm.q[qb][t] + kHalfBytes, &tmap_q, &sm.q_full[qb], 64, qi.h, qi.tok0 + t * 128);
+            const int tok = qi.tok0 + t * (128 >> pack_shift);   // a box is 128 / hb tokens x hb heads
+            tma_load_3d(sm.q[qb][t], &tmap_q, &sm.q_full[qb], 0, qi.h, tok);
+            tma_load_3d(sm.q[qb][t] + kHalfBytes, &tmap_q, &sm.q_full[qb], 64, qi.h, tok);
           }
         };
         int j = 0, j_next = 0;
@@ -455,11 +466,11 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           const bool have_next = next_item(j_next, it_next);
           if (QB == 1) load_q(it);
           if (!ok) break;
-          const int n = it.n_pages, n_pairs = (n + 1) >> 1;
+          const int n = it.n_pages, n_pairs = (it.n_walk + 1) >> 1;
           const int page_base = p.paged ? it.kv_base : 0;
           const int tok_base = p.paged ? 0 : it.kv_base;
           for (int pi = 0; pi < n_pairs && ok; ++pi, ++pair_seq) {
-            const int np = min(2, n - 2 * pi);
+            const int np = min(2, it.n_walk - 2 * pi);
             const int kq = pair_seq % NP;
             if constexpr (Cfg::kKConvert) {
               for (int e = 0; e < np && ok; ++e, ++raw_seq) {
@@ -528,9 +539,9 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         MSA_TEND(14)
         if (!ok) break;
         ++n_q;
-        const int n = it.n_pages, n_pairs = (n + 1) >> 1;
+        const int n = it.n_pages, n_pairs = (it.n_walk + 1) >> 1;
         for (int pi = 0; pi < n_pairs && ok; ++pi, ++pair_seq) {
-          const int np = min(2, n - 2 * pi);
+          const int np = min(2, it.n_walk - 2 * pi);
           const int kq = pair_seq % NP;
           MSA_TBEGIN
           ok = mbar_wait(&sm.k_full[kq], (pair_seq / NP) & 1, abort_flag);
@@ -586,9 +597,9 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       int j = 0;
       ScoreItem it;
       while (ok && next_item(j, it)) {
-        const int n = it.n_pages, n_pairs = (n + 1) >> 1;
+        const int n = it.n_pages, n_pairs = (it.n_walk + 1) >> 1;
         for (int pi = 0; pi < n_pairs && ok; ++pi, ++pair_seq) {
-          const int np = min(2, n - 2 * pi);
+          const int np = min(2, it.n_walk - 2 * pi);
           const int kq = pair_seq % NP;
           ok = mbar_wait(&sm.k_empty[kq], ((pair_seq / NP) & 1) ^ 1, abort_flag);
           for (int e = 0; e < np && ok; ++e, ++raw_seq) {

@@ -111,10 +111,11 @@ def _check_mma_storage(scale: torch.Tensor, name: str, fmt: str, mn: int, l: int
         raise TypeError(f"{name} must be a one-byte scale dtype, got {scale.dtype}")
 
 
-def _plan(cu_q: torch.Tensor, cu_k: torch.Tensor, cu_p: torch.Tensor, qo_offset, causal: bool, Hq: int, Hk: int):
+def _plan(cu_q: torch.Tensor, cu_k: torch.Tensor, cu_p: torch.Tensor, qo_offset, causal: bool, Hq: int, Hk: int,
+          max_q: int):
     """Work list of the score kernel for these prefix arrays (host copy once per distinct set of tensors)."""
     key = tuple((t.data_ptr(), t._version, tuple(t.shape)) for t in (cu_q, cu_k, cu_p)) + (
-        None if qo_offset is None else (qo_offset.data_ptr(), qo_offset._version), bool(causal), Hq, Hk)
+        None if qo_offset is None else (qo_offset.data_ptr(), qo_offset._version), bool(causal), Hq, Hk, int(max_q))
     hit = _PLAN_CACHE.get(key)
     if hit is not None:
         return hit
@@ -127,12 +128,35 @@ def _plan(cu_q: torch.Tensor, cu_k: torch.Tensor, cu_p: torch.Tensor, qo_offset,
         off = qo_offset.detach().cpu().tolist() if qo_offset is not None else [k - q for q, k in zip(ql, kl)]
     else:
         off = None
-    work = _host_plan(ql, kl, off, causal, True, Hq, Hk, tile_rows=256)[0]
+    # Requests with only a few tokens (decode): the heads of a GQA group share the 128 rows of a query tile, as the
+    # reference's packed-Q decode path does (fp4_indexer_interface.py:913-948).  hb heads x 128 / hb tokens.
+    hr = Hq // Hk
+    pow2 = hr & -hr                                       # largest power of two dividing the heads per KV head
+    need = 1 << max(0, int(max(ql + [1])) - 1).bit_length()  # tokens of the longest request, rounded up
+    hb = max(1, min(pow2, 128 // min(128, need)))
+    rows = 256 // hb
+    sms = torch.cuda.get_device_properties(cu_q.device).multi_processor_count
+    work = _host_plan(ql, kl, off, causal, True, Hq, Hk, tile_rows=rows)[0]
+    items = int(work.shape[0]) * (Hq // hb)
+    max_pages = max([(k + PAGE - 1) // PAGE for k in kl] + [0])
+    # fewer work items than SMs: cut every entry's page range (per-page maxima need no merging afterwards)
+    # into whole waves of one CTA per SM where possible, at least 16 pages per piece
+    splits, best = 1, -1.0
+    for n_s in range(1, max(1, min(max_pages // 16, 64)) + 1):
+        if items == 0 or items * n_s > 64 * sms and n_s > 1:
+            break
+        eff = items * n_s / (math.ceil(items * n_s / sms) * sms) - 0.01 * n_s
+        if eff > best:
+            splits, best = n_s, eff
+    if splits > 1:
+        work = _host_plan(ql, kl, off, causal, True, Hq, Hk, tile_rows=rows, dense_kv_splits=splits)[0]
     if work.shape[0]:
         # page-table offsets as the caller gives them (they need not be the running sum of ceil(k_len / 128))
         work[:, 6] = [cp[r] for r in work[:, 0].tolist()]
-    plan = dict(work=torch.from_numpy(work).to(cu_q.device).contiguous(), n_work=int(work.shape[0]),
-                status=torch.zeros(1, dtype=torch.int32, device=cu_q.device), max_kv=max(kl) if kl else 0)
+        work[:, 7] = 0
+    plan = dict(work=torch.from_numpy(work).to(cu_q.device).contiguous(), n_work=int(work.shape[0]), pack_heads=hb,
+                tile_rows=rows, status=torch.zeros(1, dtype=torch.int32, device=cu_q.device),
+                max_kv=max(kl) if kl else 0)
     if len(_PLAN_CACHE) > 64:
         _PLAN_CACHE.clear()
     _PLAN_CACHE[key] = plan
@@ -195,7 +219,7 @@ def fp4_indexer_block_scores(
     if max_k_tiles == 0 or total_q == 0:
         return scores
     lib = get_lib()
-    plan = _plan(cu_seqlens_q, cu_seqlens_k, cu_page_offsets, qo_offset, bool(causal), Hq, Hk)
+    plan = _plan(cu_seqlens_q, cu_seqlens_k, cu_page_offsets, qo_offset, bool(causal), Hq, Hk, int(max_seqlen_q))
     if plan["max_kv"] > max_k_tiles * PAGE:
         raise ValueError("max_seqlen_k is smaller than the longest KV segment")
     # K scales: the kernel reads the tiled storage; logical ones are tiled first (what the reference does too)
@@ -213,7 +237,8 @@ def fp4_indexer_block_scores(
     a = FmhaArgs()
     a.q, a.k, a.v = _ptr(q16), _ptr(k_bytes), None
     a.out, a.lse, a.max_score = None, None, _ptr(scores)
-    a.work, a.n_work, a.tile_rows = _ptr(plan["work"]), plan["n_work"], 256
+    a.work, a.n_work, a.tile_rows = _ptr(plan["work"]), plan["n_work"], plan["tile_rows"]
+    a.score_pack_heads = plan["pack_heads"]
     a.kv_indices = _ptr(kv_indices.contiguous())
     a.k_scale_128x4 = _ptr(k_sf)
     a.k_scale_format = _FORMAT_CODE[fmt]
