@@ -26,6 +26,10 @@ extern "C" {
 #define MSA_ERR_TIMEOUT (-3)     /* a bounded device-side wait ran out (status word) */
 #define MSA_ERR_DRIVER (-4)      /* driver entry point or tensor-map encode failed */
 #define MSA_ERR_TOO_LARGE (-5)   /* size beyond a stated maximum */
+#define MSA_ERR_BOUNDS (-6)      /* a page-table entry outside [0, kv_rows) reached a kernel (status word): the page was
+                                    replaced by page 0, so the result is wrong but nothing was read out of bounds --
+                                    the role of the reference's FMHA_GMEM_CHECK build (csrc/gmem_bounds_check.h:27-95),
+                                    always on here because it costs one compare per page */
 /* msa_validate_inputs: the first rule of the index contract that the inputs break */
 #define MSA_EVAL_Q_ROWS (-101)            /* q rows != sum(qo_lens) */
 #define MSA_EVAL_KV_ROWS (-102)           /* ragged K/V rows != sum(kv_lens) */
@@ -174,7 +178,8 @@ typedef struct msa_fmha_args {
   float qk_scale;         /* q_scale * k_scale (* k global scale for nvfp4) */
   float v_scale;          /* v_scale * o_scale (* v global scale for nvfp4) */
   int32_t* status;        /* device int32, zeroed by the caller; receives MSA_ERR_TIMEOUT if a wait ran out,
-                             MSA_ERR_UNSUPPORTED for a request beyond the page-list limit above */
+                             MSA_ERR_UNSUPPORTED for a request beyond the page-list limit above, MSA_ERR_BOUNDS for
+                             a page-table entry outside [0, kv_rows) */
   int32_t max_ctas;       /* > 0 caps the persistent grid (the reference's usable_SM_count); 0 = one CTA per SM */
   int32_t qk_dim;         /* 0 or 128: all of the head dimension; 64: the score-only pass (out = NULL) uses only the
                              first 64 elements of q and k (a 64-wide proxy zero-padded to 128 costs half) */

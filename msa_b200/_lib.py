@@ -21,6 +21,7 @@ SOURCES = ["abi.cu", "topk.cu", "decode.cu", "fmha_host.cu", "kv_quant.cu", "pla
 
 MSA_KV_BF16, MSA_KV_FP8_E4M3, MSA_KV_NVFP4 = 0, 1, 2
 MSA_ERR_TIMEOUT = -3
+MSA_ERR_BOUNDS = -6
 ABI_VERSION = 3
 
 

@@ -13,6 +13,7 @@ const char* msa_error_string(int code) {
     case MSA_ERR_TIMEOUT: return "device-side wait timed out";
     case MSA_ERR_DRIVER: return "CUDA driver entry point or tensor map encode failed";
     case MSA_ERR_TOO_LARGE: return "size beyond the supported maximum";
+    case MSA_ERR_BOUNDS: return "a page-table entry outside the K/V page pool reached a kernel";
     case MSA_EVAL_Q_ROWS: return "sum(qo_segment_lens) != q.shape[0]";
     case MSA_EVAL_KV_ROWS: return "sum(kv_segment_lens) != k.shape[0]";
     case MSA_EVAL_PAGE_TABLE_LENGTH: return "kv_indices length != sum(ceil(kv_segment_lens / page_size))";

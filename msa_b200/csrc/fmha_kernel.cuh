@@ -77,6 +77,7 @@ struct FmhaParams {
   int k_scale_tile_bytes;        // score-only pass over packed e2m1 K: scale bytes per (page, head): 1024 (e4m3 per 16
                                  // values) or 512 (ue8m0 per 32 values, k_mx)
   int k_mx;
+  int kv_pages;                  // paged K/V: physical pages in the pool (page-table entries are checked against it)
   int pack_heads;                // score-only pass: query heads per 128-row tile (a power of two dividing hr), else 1
   const uint8_t* k_raw;          // NVFP4 raw page storage
   const uint8_t* v_raw;
@@ -1014,7 +1015,12 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const int tok_base = p.paged ? 0 : info.kv_base;
         // K (and V) of one page into the next ring slots (lane 0)
         auto load_page = [&](int page) {
-          const int phys = p.paged ? __ldg(p.kv_indices + page_base + page) : 0;
+          int phys = p.paged ? __ldg(p.kv_indices + page_base + page) : 0;
+          if (static_cast<unsigned>(phys) >= static_cast<unsigned>(p.kv_pages) && p.paged) {
+            // a corrupt page table: report it and read page 0 instead of memory outside the pool
+            atomicExch(p.status, MSA_ERR_BOUNDS);
+            phys = 0;
+          }
           const int tok_k = tok_base + (page << 7);
           const size_t tile = static_cast<size_t>(phys) * p.Hkv + info.g;
           // ---- K ----

@@ -475,7 +475,11 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             if constexpr (Cfg::kKConvert) {
               for (int e = 0; e < np && ok; ++e, ++raw_seq) {
                 const int page = n - 1 - (2 * pi + e);
-                const int phys = __ldg(p.kv_indices + page_base + page);
+                int phys = __ldg(p.kv_indices + page_base + page);
+                if (static_cast<unsigned>(phys) >= static_cast<unsigned>(p.kv_pages)) {
+                  atomicExch(p.status, MSA_ERR_BOUNDS);   // corrupt page table: reported, page 0 read instead
+                  phys = 0;
+                }
                 const size_t tile = static_cast<size_t>(phys) * p.Hkv + it.g;
                 const int s = raw_seq % NRAW;
                 MSA_TBEGIN
@@ -495,7 +499,11 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
               mbar_expect_tx(&sm.k_full[kq], np * (fp8_half ? Cfg::kPageBytes / 2 : Cfg::kPageBytes));
               for (int e = 0; e < np; ++e) {
                 const int page = n - 1 - (2 * pi + e);
-                const int phys = p.paged ? __ldg(p.kv_indices + page_base + page) : 0;
+                int phys = p.paged ? __ldg(p.kv_indices + page_base + page) : 0;
+                if (p.paged && static_cast<unsigned>(phys) >= static_cast<unsigned>(p.kv_pages)) {
+                  atomicExch(p.status, MSA_ERR_BOUNDS);
+                  phys = 0;
+                }
                 const int tok_k = tok_base + (page << 7);
                 uint8_t* kdst = sm.k + kq * pair_bytes + e * page_stride;
                 if constexpr (Cfg::kKDirectFp8) {

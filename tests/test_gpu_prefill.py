@@ -555,3 +555,22 @@ def test_sparse_atten_func_temperature_lse():
         msa_b200.sparse_atten_func(q.cuda(), kp.cuda(), vp.cuda(), rp, qi, topk, cu_seqlens_q=cu_q.cuda(),
                                    cu_seqlens_k=cu_k_cap.cuda(), max_seqlen_q=max(qo), max_seqlen_k=max(kv),
                                    causal=True, return_temperature_lse=True, page_table=pt.cuda())
+
+
+def test_corrupt_page_table_is_reported_not_followed():
+    """A page-table entry beyond the page pool: the kernel reads page 0 instead, finishes normally and the status
+    word reads MSA_ERR_BOUNDS (what the reference's FMHA_GMEM_CHECK build reports, csrc/gmem_bounds_check.h:27-95).
+    Nothing is read out of bounds, so nothing faults; a clean call on the same plan then reads status 0 again."""
+    kv_lens = [700]
+    kp, vp, table = make_paged(kv_lens, 2, 51)
+    q = torch.randn(64, 4, 128, generator=torch.Generator().manual_seed(52)).to(torch.bfloat16)
+    plan = msa_b200.fmha_sm100_plan(torch.tensor([64]), torch.tensor(kv_lens), 4, num_kv_heads=2, page_size=128,
+                                    output_maxscore=True)
+    bad = table.clone()
+    bad[2] = kp.shape[0] + 5
+    for kwargs in (dict(output_o=True, output_maxscore=False), dict(output_o=False, output_maxscore=True)):
+        msa_b200.fmha_sm100(q.cuda(), kp.cuda(), vp.cuda(), plan, kv_indices=bad.cuda(), **kwargs)
+        assert msa_b200.plan_status(plan) == msa_b200._lib.MSA_ERR_BOUNDS
+        plan[3]["status"].zero_()
+        msa_b200.fmha_sm100(q.cuda(), kp.cuda(), vp.cuda(), plan, kv_indices=table.cuda(), **kwargs)
+        assert msa_b200.plan_status(plan) == 0
