@@ -944,6 +944,19 @@ def main():
                                             "tflops_score_only_causal": c2["flops_score"] / (mo * 1e-3) / 1e12}
         del c2
         torch.cuda.empty_cache()
+        # FP4 indexer on the shapes of the reference's published table (its own kernel beside it:
+        # `--stage fp4_indexer`, which pays the reference's JIT compile)
+        fp4 = []
+        for case in FP4_CASES:
+            for fmt in ("nvfp4", "mxfp4"):
+                try:
+                    r = fp4_indexer_stage(dev, fmt, case, False)
+                    fp4.append({"case": case, "format": fmt, "ms": r["ours"]["ms"],
+                                "tflops_effective": r["ours"]["tflops_effective"]})
+                except Exception as e:  # noqa: BLE001
+                    fp4.append({"case": case, "format": fmt, "error": f"{type(e).__name__}: {e}"[:200]})
+                torch.cuda.empty_cache()
+        stages["fp4_indexer"] = fp4
         c5 = build_nvfp4_c5(dev)
         m5, _ = time_fn(c5["run"], 5, 2)
         stages["nvfp4_prefill_c5_one_gpu_share"] = {"ms": m5, "tflops_effective": c5["flops"] / (m5 * 1e-3) / 1e12,
