@@ -99,7 +99,7 @@ int make_paged_e4m3_map(void* tensor_map, const void* kv, int64_t pages, int hkv
 static long long* g_timing_buffer = nullptr;
 void set_timing_buffer(void* ptr) { g_timing_buffer = static_cast<long long*>(ptr); }
 
-template <int NT, int KVMODE, bool SCORE, int LISTS>
+template <int NT, int KVMODE, int LISTS>
 static int launch_fmha_mode(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
                        const FmhaParams& p, int max_ctas, cudaStream_t st) {
   using Cfg = FmhaCfg<NT, KVMODE>;
@@ -107,12 +107,12 @@ static int launch_fmha_mode(const CUtensorMap& mq, const CUtensorMap& mk, const 
   int num_sms = 0;
   constexpr int smem = fmha_smem_bytes<NT, KVMODE>();
   const int rc = setup.ensure(&num_sms, [] {
-    cudaError_t e = cudaFuncSetAttribute(fmha_fwd_kernel<NT, KVMODE, SCORE, LISTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(fmha_fwd_kernel<NT, KVMODE, LISTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
     if (Cfg::kRebalance) {
       // the in-kernel register hand-over only balances if the CTA starts with exactly kRegsLaunch per thread
       cudaFuncAttributes fa;
-      e = cudaFuncGetAttributes(&fa, fmha_fwd_kernel<NT, KVMODE, SCORE, LISTS>);
+      e = cudaFuncGetAttributes(&fa, fmha_fwd_kernel<NT, KVMODE, LISTS>);
       if (e != cudaSuccess) return static_cast<int>(e);
       if (fa.numRegs != Cfg::kRegsLaunch) return static_cast<int>(MSA_ERR_UNSUPPORTED);
     }
@@ -122,7 +122,7 @@ static int launch_fmha_mode(const CUtensorMap& mq, const CUtensorMap& mk, const 
   // persistent: one CTA per SM walks the item list with stride gridDim.x; max_ctas > 0 caps the grid
   int ctas = p.n_items < num_sms ? p.n_items : num_sms;
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
-  fmha_fwd_kernel<NT, KVMODE, SCORE, LISTS><<<static_cast<unsigned>(ctas), Cfg::kThreads, smem, st>>>(mq, mk, mv, mo, p);
+  fmha_fwd_kernel<NT, KVMODE, LISTS><<<static_cast<unsigned>(ctas), Cfg::kThreads, smem, st>>>(mq, mk, mv, mo, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -155,8 +155,8 @@ static int launch_score(const CUtensorMap& mq, const CUtensorMap& mk, const Fmha
 template <int NT, int KVMODE>
 static int launch_fmha(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
                        const FmhaParams& p, int max_ctas, cudaStream_t st) {
-  return p.sparse ? launch_fmha_mode<NT, KVMODE, false, 1>(mq, mk, mv, mo, p, max_ctas, st)
-                  : launch_fmha_mode<NT, KVMODE, false, 0>(mq, mk, mv, mo, p, max_ctas, st);
+  return p.sparse ? launch_fmha_mode<NT, KVMODE, 1>(mq, mk, mv, mo, p, max_ctas, st)
+                  : launch_fmha_mode<NT, KVMODE, 0>(mq, mk, mv, mo, p, max_ctas, st);
 }
 
 int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
@@ -235,7 +235,6 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
   if (score_only) nt = hb;  // the score kernel takes hb heads per work item
   p.pack_heads = hb;
   p.kv_pages = a->paged ? static_cast<int>(a->kv_rows < 0x7fffffffLL ? a->kv_rows : 0x7fffffffLL) : 0;
-  p.pair_tiles = 0;
   p.n_head_groups = p.Hq / nt;
   const long long n_items = static_cast<long long>(p.n_work) * p.n_head_groups;
   if (n_items > 0x7fffffffLL) return MSA_ERR_TOO_LARGE;

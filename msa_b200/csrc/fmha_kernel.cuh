@@ -1,6 +1,6 @@
 // Paged attention forward for sm_100a: one persistent kernel covers the dense pass
-// (with or without per-page max score), the score-only proxy pass and the
-// block-sparse pass over the pages each query token selected.
+// (with or without per-page max score) and the block-sparse pass over the pages each
+// query token selected.  (The score-only proxy pass is score_kernel.cuh.)
 //
 // One CTA per SM loops over work items; an item is one 128-token query tile x NT
 // query heads of one KV group.  Roles (warps):
@@ -83,9 +83,7 @@ struct FmhaParams {
   const uint8_t* v_raw;
   int Hq, Hkv, hr, topk, list_heads, total_q, max_k_tiles, n_work, n_head_groups, n_items;
   int causal, paged, sparse, do_pv, do_maxscore;
-  int half_dim;                  // score-only pass over the first 64 of the 128 head-dim elements
-  int pair_tiles;                // score-only pass: the two tiles of a CTA are the 128-row halves of one 256-row work
-                                 // entry of ONE head (instead of two heads of one 128-row entry)
+  int half_dim;                  // score kernel: only the first 64 of the 128 head-dim elements count
   float scale_log2;              // softmax scale * log2(e) * (q_scale * k_scale [* k_global])
   float out_scale;               // v_scale * o_scale [* v_global]
   int* status;
@@ -102,9 +100,6 @@ struct FmhaCfg {
   static constexpr int kKBytes = kKDirectFp8 ? kHalfBytes : kTileBytes;
   static constexpr int kKStages = 2;
   static constexpr int kVStages = 2;
-  // Score-only pass (no V, nothing converted): the V tiles' shared memory serves as further K stages, because
-  // with one K page per step and no P.V to hide behind, the depth of the K ring is what covers the load latency.
-  static constexpr int kKStagesScore = kKConvert ? kKStages : kKStages + kVStages * kTileBytes / kKBytes;
   static constexpr int kRawStages = kQuant ? 2 : 0;
   static constexpr int kRawBytes = KVMODE == KV_NVFP4 ? 10240 : 16384;
   static constexpr int kSoftmaxWarps = 4 * NT;
@@ -145,12 +140,10 @@ struct __align__(1024) FmhaSmem {
   // rows that lie num_qo_heads * 256 bytes apart
   alignas(1024) uint8_t o_stage[Cfg::kStageOut ? Cfg::kSoftmaxWarps : 1][Cfg::kStageOut ? 2048 : 16];
   uint64_t q_full, q_ready, q_empty;
-  uint64_t k_full[Cfg::kKStagesScore], k_empty[Cfg::kKStagesScore];
+  uint64_t k_full[Cfg::kKStages], k_empty[Cfg::kKStages];
   uint64_t v_full[Cfg::kVStages], v_empty[Cfg::kVStages];
   uint64_t raw_full[Cfg::kRawStages > 0 ? Cfg::kRawStages : 1], raw_empty[Cfg::kRawStages > 0 ? Cfg::kRawStages : 1];
   uint64_t s_full[NT], p_full[NT], o_final[NT];
-  // score-only pass: S is double-buffered (the O columns are free), one barrier pair per buffer
-  uint64_t sc_full[NT][2], sc_free[NT][2];
   uint64_t bm_full[2], bm_empty[2];
   uint32_t tmem_base;
   int abort;
@@ -224,7 +217,7 @@ __device__ __forceinline__ ItemInfo decode_item(const FmhaParams& p, int item, i
   it.page_lo = SPLITS ? (w.z >> 10) : 0;
   it.out_off = SPLITS ? w2.w : 0;
   it.qloc0 = w.w;
-  it.h0 = p.pair_tiles ? hg : hg * nt;
+  it.h0 = hg * nt;
   it.g = it.h0 / p.hr;
   it.kv_len = w2.x;
   it.qo_off = w2.y;
@@ -325,26 +318,21 @@ __device__ __forceinline__ void e4m3x2_to_f32x2(uint32_t v, float& a, float& b) 
 // TMEM addresses are absolute: the kernel owns all 512 columns, so the allocation starts at column 0.
 // S_T (+ d_off columns) = Q_T K^T with the K tile at shared-memory address k_saddr
 template <class Cfg, class Smem, int T>
-__device__ __forceinline__ void issue_qk_at(Smem& sm, uint32_t k_saddr, uint32_t d_off = 0, bool half_dim = false) {
+__device__ __forceinline__ void issue_qk_at(Smem& sm, uint32_t k_saddr) {
   constexpr uint32_t desc_hi = smem_desc_hi(1024);
   const uint32_t qa = smem_desc_lo(smem_u32(sm.q[T]), 16), ka = smem_desc_lo(k_saddr, 16);
-  const uint32_t d = T * 128 + d_off;
+  constexpr uint32_t d = T * 128;
   if constexpr (Cfg::kKDirectFp8) {
     // S = Q_hi K^T + Q_lo K^T: 2 x 4 steps of 32 contraction bytes inside the 128-byte swizzle row
-    // (2 x 2 steps when only the first 64 elements count)
     constexpr uint32_t idesc = make_idesc(128, 128, 0, 0, 0, 0);
     umma_ss_lohi<0, 1>(d, qa, ka, desc_hi, idesc);
     umma_ss_lohi<1, 1>(d, qa + 2, ka + 2, desc_hi, idesc);
-    if (!half_dim) {
-      umma_ss_lohi<1, 1>(d, qa + 4, ka + 4, desc_hi, idesc);
-      umma_ss_lohi<1, 1>(d, qa + 6, ka + 6, desc_hi, idesc);
-    }
+    umma_ss_lohi<1, 1>(d, qa + 4, ka + 4, desc_hi, idesc);
+    umma_ss_lohi<1, 1>(d, qa + 6, ka + 6, desc_hi, idesc);
     umma_ss_lohi<1, 1>(d, qa + 1024, ka, desc_hi, idesc);
     umma_ss_lohi<1, 1>(d, qa + 1026, ka + 2, desc_hi, idesc);
-    if (!half_dim) {
-      umma_ss_lohi<1, 1>(d, qa + 1028, ka + 4, desc_hi, idesc);
-      umma_ss_lohi<1, 1>(d, qa + 1030, ka + 6, desc_hi, idesc);
-    }
+    umma_ss_lohi<1, 1>(d, qa + 1028, ka + 4, desc_hi, idesc);
+    umma_ss_lohi<1, 1>(d, qa + 1030, ka + 6, desc_hi, idesc);
   } else {
     // the first 64 elements are the first 128-byte swizzle sub-tile
     constexpr uint32_t idesc = make_idesc(128, 128, Cfg::kFmt16, Cfg::kFmt16, 0, 0);
@@ -352,12 +340,10 @@ __device__ __forceinline__ void issue_qk_at(Smem& sm, uint32_t k_saddr, uint32_t
     umma_ss_lohi<1, 0>(d, qa + 2, ka + 2, desc_hi, idesc);
     umma_ss_lohi<1, 0>(d, qa + 4, ka + 4, desc_hi, idesc);
     umma_ss_lohi<1, 0>(d, qa + 6, ka + 6, desc_hi, idesc);
-    if (!half_dim) {
-      umma_ss_lohi<1, 0>(d, qa + 1024, ka + 1024, desc_hi, idesc);
-      umma_ss_lohi<1, 0>(d, qa + 1026, ka + 1026, desc_hi, idesc);
-      umma_ss_lohi<1, 0>(d, qa + 1028, ka + 1028, desc_hi, idesc);
-      umma_ss_lohi<1, 0>(d, qa + 1030, ka + 1030, desc_hi, idesc);
-    }
+    umma_ss_lohi<1, 0>(d, qa + 1024, ka + 1024, desc_hi, idesc);
+    umma_ss_lohi<1, 0>(d, qa + 1026, ka + 1026, desc_hi, idesc);
+    umma_ss_lohi<1, 0>(d, qa + 1028, ka + 1028, desc_hi, idesc);
+    umma_ss_lohi<1, 0>(d, qa + 1030, ka + 1030, desc_hi, idesc);
   }
 }
 template <class Cfg, class Smem, int T, int S>
@@ -373,14 +359,14 @@ __device__ __forceinline__ void issue_pv_static(Smem& sm, uint32_t accumulate) {
 }
 // same with the ring stage known at the call site, so that the addresses are constants plus the buffer base
 template <class Cfg, class Smem, int T, int S>
-__device__ __forceinline__ void issue_qk_static(Smem& sm, uint32_t d_off = 0, bool half_dim = false) {
-  issue_qk_at<Cfg, Smem, T>(sm, smem_u32(sm.k[S]), d_off, half_dim);
+__device__ __forceinline__ void issue_qk_static(Smem& sm) {
+  issue_qk_at<Cfg, Smem, T>(sm, smem_u32(sm.k[S]));
 }
 template <class Cfg, class Smem, int T>
-__device__ __forceinline__ void issue_qk_stage(Smem& sm, int stage, uint32_t d_off = 0, bool half_dim = false) {
-  if (stage == 0) issue_qk_static<Cfg, Smem, T, 0>(sm, d_off, half_dim);
-  else if (stage == 1) issue_qk_static<Cfg, Smem, T, 1>(sm, d_off, half_dim);
-  else if constexpr (Cfg::kKStages > 2) issue_qk_static<Cfg, Smem, T, 2>(sm, d_off, half_dim);
+__device__ __forceinline__ void issue_qk_stage(Smem& sm, int stage) {
+  if (stage == 0) issue_qk_static<Cfg, Smem, T, 0>(sm);
+  else if (stage == 1) issue_qk_static<Cfg, Smem, T, 1>(sm);
+  else if constexpr (Cfg::kKStages > 2) issue_qk_static<Cfg, Smem, T, 2>(sm);
 }
 template <class Cfg, class Smem, int T>
 __device__ __forceinline__ void issue_pv_stage(Smem& sm, int stage, uint32_t accumulate) {
@@ -388,23 +374,20 @@ __device__ __forceinline__ void issue_pv_stage(Smem& sm, int stage, uint32_t acc
   else issue_pv_static<Cfg, Smem, T, 1>(sm, accumulate);
 }
 
-// SCORE: the score-only pass (per-page max of Q K^T, no softmax, no V) as a kernel of its own, so that neither
-// variant carries the other's code
+// (The score-only pass, per-page max of Q K^T with no softmax and no V, is a kernel of its own: score_kernel.cuh.)
 // LISTS: 0 = no page lists (dense walk only), 1 = decided at run time by p.sparse (the variant page-list calls
 // use).  The dense specialisation is measurably faster than the generic code on dense calls, while the
 // generic code is the faster one on page-list calls, so each kind of call gets its own instantiation.
-template <int NT, int KVMODE, bool SCORE, int LISTS>
+template <int NT, int KVMODE, int LISTS>
 __global__ void __launch_bounds__(FmhaCfg<NT, KVMODE>::kThreads, 1)
 fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
                 const FmhaParams p) {
   using Cfg = FmhaCfg<NT, KVMODE>;
   using Smem = FmhaSmem<NT, KVMODE>;
-  constexpr int NK = Cfg::kKStages, NV = Cfg::kVStages, NKS = Cfg::kKStagesScore;
-  constexpr bool kDoPv = !SCORE;
-  constexpr bool kSplits = !SCORE && LISTS == 0;   // only dense calls with output are ever planned with KV splits
+  constexpr int NK = Cfg::kKStages, NV = Cfg::kVStages;
+  constexpr bool kSplits = LISTS == 0;   // only dense calls are ever planned with KV splits
   const bool sparse = LISTS != 0 && p.sparse != 0;
-  const bool pair_tiles = SCORE && p.pair_tiles != 0;
   constexpr int NRAW = Cfg::kRawStages > 0 ? Cfg::kRawStages : 1;
   extern __shared__ uint8_t smem_raw[];
   Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -420,7 +403,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     mbar_init(&sm.q_full, 1);
     mbar_init(&sm.q_ready, 4 * NT);              // one arrival per softmax warp
     mbar_init(&sm.q_empty, 1);
-    for (int s = 0; s < NKS; ++s) {
+    for (int s = 0; s < NK; ++s) {
       mbar_init(&sm.k_full[s], Cfg::kKConvert ? Cfg::kCvtThreads / 32 : 1);
       mbar_init(&sm.k_empty[s], 1);
     }
@@ -436,10 +419,6 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       mbar_init(&sm.s_full[t], 1);
       mbar_init(&sm.p_full[t], 128);              // every softmax thread arrives (measured faster than one per warp)
       mbar_init(&sm.o_final[t], 1);
-      for (int b2 = 0; b2 < 2; ++b2) {
-        mbar_init(&sm.sc_full[t][b2], 1);
-        mbar_init(&sm.sc_free[t][b2], 4);
-      }
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&sm.bm_full[b], 1);
@@ -465,11 +444,6 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   // the MMA warp addresses TMEM absolutely (all 512 columns are ours, so the base can only be column 0)
   if (tmem != 0 && tid == 0) sm.abort = 1;
   __syncthreads();
-  // K ring in effect: deeper in the score-only pass, where stages beyond the first NK live in the V tiles' memory
-  constexpr int nk_ring = SCORE ? NKS : NK;
-  auto k_stage_ptr = [&](int st) -> uint8_t* {
-    return st < NK ? sm.k[st] : &sm.v[0][0] + static_cast<size_t>(st - NK) * Cfg::kKBytes;
-  };
   // The j-th item of this CTA, or -1 past the end.  The list is ordered heaviest first and the CTAs walk it in
   // rounds of gridDim.x items, forwards in even rounds and backwards in odd ones (a snake), so that the CTA
   // that drew the heaviest item of one round draws the lightest of the next.
@@ -537,7 +511,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       } else {
         nx.info = load_item<kSplits>(p, item, NT);
       }
-      const int r_tile = pair_tiles ? t * 128 + r : r;   // my row within the work entry
+      const int r_tile = r;   // my row within the work entry
       nx.row_valid = r_tile < nx.info.rows;
       nx.limit_base = -1;
       nx.list = nullptr;
@@ -656,7 +630,6 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     auto epilogue = [&]() {
       if (!pend.valid) return;
       pend.valid = false;
-      if (!kDoPv) return;
       if (pend.n_iter > 0) {
         ok = ok && mbar_wait(&sm.o_final[t], n_fin & 1, abort_flag);
         ++n_fin;
@@ -733,8 +706,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       if (j >= 0) {
       // ---- main loop of the item prepared in nx -------------------------------
       const ItemInfo info = nx.info;
-      const int h = pair_tiles ? info.h0 : info.h0 + t;
-      const int tok = info.tok0 + (pair_tiles ? t * 128 + r : r);
+      const int h = info.h0 + t;
+      const int tok = info.tok0 + r;
       const bool row_valid = nx.row_valid;
       const int limit_base = nx.limit_base;
       const int* list = nx.list;
@@ -761,18 +734,15 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
         const bool full_vis = __all_sync(0xffffffffu, limit >= 127);
 
-        // score-only pass: the S tiles alternate between columns [t*128, +128) and the O columns 256 further
-        const int sb = kDoPv ? 0 : static_cast<int>(it_total & 1);
         MSA_TBEGIN
-        ok = kDoPv ? mbar_wait(&sm.s_full[t], it_total & 1, abort_flag)
-                     : mbar_wait(&sm.sc_full[t][sb], (it_total >> 1) & 1, abort_flag);
+        ok = mbar_wait(&sm.s_full[t], it_total & 1, abort_flag);
         MSA_TEND(0)
         if (!ok) break;
         tc_fence_after();
         if (releaser) {
-          mbar_arrive(&sm.k_empty[k_rel % nk_ring]);
+          mbar_arrive(&sm.k_empty[k_rel % NK]);
           ++k_rel;
-          if (kDoPv && n_iter > 0) {
+          if (n_iter > 0) {
             mbar_arrive(&sm.v_empty[v_rel % NV]);
             ++v_rel;
           }
@@ -782,18 +752,11 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 
         // the whole 128-column S row of this thread, one wait for the four loads
         uint32_t sr[128];
-        const uint32_t s_cur = s_addr + sb * 256;
-        tmem_ld32p(s_cur, sr);
-        tmem_ld32p(s_cur + 32, sr + 32);
-        tmem_ld32p(s_cur + 64, sr + 64);
-        tmem_ld32p(s_cur + 96, sr + 96);
+        tmem_ld32p(s_addr, sr);
+        tmem_ld32p(s_addr + 32, sr + 32);
+        tmem_ld32p(s_addr + 64, sr + 64);
+        tmem_ld32p(s_addr + 96, sr + 96);
         tmem_ld_wait();
-        if (!kDoPv) {
-          // score-only pass: S is in registers, the MMA warp may overwrite this buffer
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&sm.sc_free[t][sb]);
-        }
         if (!full_vis) {
 #pragma unroll
           for (int c = 0; c < 128; ++c) sr[c] = (c <= limit) ? sr[c] : 0xff800000u;
@@ -810,58 +773,56 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         if (p.do_maxscore && row_valid)
           __stwt(p.max_score + h * p.ms_head + page * p.ms_tile + tok, tmax * ms_scale);
 
-        if (kDoPv) {
-          const float m_new = fmaxf(m_used, tmax);
-          const bool first = (m_used == -INFINITY);
-          const bool need = !first && ((m_new - m_used) * sl2 > kRescaleThreshold);
-          if (__any_sync(0xffffffffu, need)) {
-            // every MMA issued before the one that produced this S tile has completed, so O is quiescent;
-            // eight columns at a time keeps the S row resident in registers
-            const float alpha = need ? fast_exp2((m_used - m_new) * sl2) : 1.0f;
+        const float m_new = fmaxf(m_used, tmax);
+        const bool first = (m_used == -INFINITY);
+        const bool need = !first && ((m_new - m_used) * sl2 > kRescaleThreshold);
+        if (__any_sync(0xffffffffu, need)) {
+          // every MMA issued before the one that produced this S tile has completed, so O is quiescent;
+          // eight columns at a time keeps the S row resident in registers
+          const float alpha = need ? fast_exp2((m_used - m_new) * sl2) : 1.0f;
 #pragma unroll 1
-            for (int c = 0; c < 16; ++c) {
-              uint32_t rg[8];
-              tmem_ld8(o_addr + c * 8, rg);
-              tmem_ld_wait();
+          for (int c = 0; c < 16; ++c) {
+            uint32_t rg[8];
+            tmem_ld8(o_addr + c * 8, rg);
+            tmem_ld_wait();
 #pragma unroll
-              for (int e = 0; e < 8; ++e) rg[e] = __float_as_uint(__uint_as_float(rg[e]) * alpha);
-              tmem_st8(o_addr + c * 8, rg);
-            }
-            l_sum *= alpha;
+            for (int e = 0; e < 8; ++e) rg[e] = __float_as_uint(__uint_as_float(rg[e]) * alpha);
+            tmem_st8(o_addr + c * 8, rg);
           }
-          if (need || first) m_used = m_new;
-          const float mb = (m_used == -INFINITY) ? 0.f : m_used * sl2;
-
-          // P = exp2(S * scale - m * scale) -> 16-bit pairs into the first 64 columns of S (packed fp32 math);
-          // each S register dies as its exponential is taken
-          const uint64_t sl2_2 = pack2(sl2, sl2), nmb_2 = pack2(kBias - mb, kBias - mb);
-          uint64_t acc = 0ull;
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            uint32_t pk[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const int col = c * 16 + 2 * e;
-              float x0, x1;
-              unpack2(fma2(pack2u(sr[col], sr[col + 1]), sl2_2, nmb_2), x0, x1);
-              const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-              acc = add2(acc, pack2(p0, p1));
-              pk[e] = Cfg::kQuant ? __byte_perm(__float_as_uint(p0) >> 13, __float_as_uint(p1) >> 13, 0x5410)
-                                  : __byte_perm(__float_as_uint(p0), __float_as_uint(p1), 0x7632);
-            }
-            tmem_st8(s_addr + c * 8, pk);
-          }
-          {
-            float a0, a1;
-            unpack2(acc, a0, a1);
-            l_sum += a0 + a1;
-          }
-          tmem_st_wait();
-          tc_fence_before();
-          mbar_arrive(&sm.p_full[t]);
-          if (r == 0) { MSA_TRACE(t * 2 + 1, it_total, clock64()) }
+          l_sum *= alpha;
         }
-        MSA_TEND(1)
+        if (need || first) m_used = m_new;
+        const float mb = (m_used == -INFINITY) ? 0.f : m_used * sl2;
+
+        // P = exp2(S * scale - m * scale) -> 16-bit pairs into the first 64 columns of S (packed fp32 math);
+        // each S register dies as its exponential is taken
+        const uint64_t sl2_2 = pack2(sl2, sl2), nmb_2 = pack2(kBias - mb, kBias - mb);
+        uint64_t acc = 0ull;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint32_t pk[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int col = c * 16 + 2 * e;
+            float x0, x1;
+            unpack2(fma2(pack2u(sr[col], sr[col + 1]), sl2_2, nmb_2), x0, x1);
+            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+            acc = add2(acc, pack2(p0, p1));
+            pk[e] = Cfg::kQuant ? __byte_perm(__float_as_uint(p0) >> 13, __float_as_uint(p1) >> 13, 0x5410)
+                                : __byte_perm(__float_as_uint(p0), __float_as_uint(p1), 0x7632);
+          }
+          tmem_st8(s_addr + c * 8, pk);
+        }
+        {
+          float a0, a1;
+          unpack2(acc, a0, a1);
+          l_sum += a0 + a1;
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&sm.p_full[t]);
+        if (r == 0) { MSA_TRACE(t * 2 + 1, it_total, clock64()) }
+                MSA_TEND(1)
       }
       // this item's bitmap is no longer needed by my warp
       if (sparse) {
@@ -1002,7 +963,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
               MSA_TRACE(13, pg_total, clock64())
               mbar_expect_tx(&sm.q_full, NT * kTileBytes);
               for (int t = 0; t < NT; ++t) {
-                const int qh = pair_tiles ? info.h0 : info.h0 + t, qt = pair_tiles ? info.tok0 + t * 128 : info.tok0;
+                const int qh = info.h0 + t, qt = info.tok0;
                 tma_load_3d(sm.q[t], &tmap_q, &sm.q_full, 0, qh, qt);
                 tma_load_3d(sm.q[t] + kHalfBytes, &tmap_q, &sm.q_full, 64, qh, qt);
               }
@@ -1033,10 +994,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             bulk_load(sm.raw[s], p.k_raw + tile * 8192, 8192, &sm.raw_full[s]);
             bulk_load(sm.raw[s] + 8192, p.k_scale_bytes + tile * 1024, 1024, &sm.raw_full[s]);
           } else {
-            const int s = k_seq % nk_ring;
-            uint8_t* kdst = k_stage_ptr(s);
+            const int s = k_seq % NK;
+            uint8_t* kdst = sm.k[s];
             MSA_TBEGIN
-            ok = mbar_wait(&sm.k_empty[s], ((k_seq / nk_ring) & 1) ^ 1, abort_flag);
+            ok = mbar_wait(&sm.k_empty[s], ((k_seq / NK) & 1) ^ 1, abort_flag);
             MSA_TEND(13)
             if (!ok) return;
             ++k_seq;
@@ -1054,7 +1015,6 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
               tma_load_3d(kdst + kHalfBytes, &tmap_k, &sm.k_full[s], 64, info.g, tok_k);
             }
           }
-          if (!kDoPv) return;
           // ---- V ----
           if constexpr (Cfg::kVConvert) {
             const int s = raw_seq % NRAW;
@@ -1139,37 +1099,6 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           MSA_TEND(14)
           if (lane == 0) { MSA_TRACE(14, it_total, clock64()) }
           ++n_q;
-          if (!kDoPv) {
-            // Score-only pass: nothing but Q K^T, one page after the other into alternating S buffers; the
-            // buffer of page n is free once the softmax warps have read page n - 2 out of it.
-            for (int i = 0; i < count && ok; ++i, ++it_total) {
-              const int ks = k_seq % nk_ring;
-              MSA_TBEGIN
-              ok = mbar_wait(&sm.k_full[ks], (k_seq / nk_ring) & 1, abort_flag);
-              MSA_TEND(6)
-              ++k_seq;
-              const int sb = it_total & 1;
-#pragma unroll
-              for (int t = 0; t < NT; ++t)
-                if (ok && it_total >= 2) ok = mbar_wait(&sm.sc_free[t][sb], ((it_total >> 1) + 1) & 1, abort_flag);
-              if (!ok) break;
-              tc_fence_after();
-              if (lane == 0) {
-                const uint32_t kaddr = smem_u32(k_stage_ptr(ks));
-                issue_qk_at<Cfg, Smem, 0>(sm, kaddr, sb * 256, p.half_dim != 0);
-                umma_commit(&sm.sc_full[0][sb]);
-                if constexpr (NT == 2) {
-                  issue_qk_at<Cfg, Smem, NT - 1>(sm, kaddr, sb * 256, p.half_dim != 0);
-                  umma_commit(&sm.sc_full[NT - 1][sb]);
-                }
-                if (i + 1 == count) umma_commit(&sm.q_empty);   // Q is free after the item's last QK
-              }
-              __syncwarp();
-            }
-            if (sparse && lane == 0) mbar_arrive(&sm.bm_empty[b]);
-            __syncwarp();
-            continue;
-          }
           // Pass i = -1 has no P to wait for and only issues S_t(0) = Q_t K(0)^T, so that every MMA group has a
           // single issue site; pass i issues O_t += P_t(i) V(i) and S_t(i + 1) = Q_t K(i + 1)^T.
           for (int i = -1; i < count && ok; ++i) {
@@ -1177,7 +1106,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             const bool has_next = i + 1 < count;
             int v_stage = 0, k_stage = 0;
             uint32_t k_this = 0;
-            if (real && kDoPv) {
+            if (real) {
               v_stage = v_seq % NV;
               MSA_TBEGIN
               ok = mbar_wait(&sm.v_full[v_stage], (v_seq / NV) & 1, abort_flag);
@@ -1207,7 +1136,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
               tc_fence_after();
               if (lane == 0) {
                 MSA_TRACE(4 + t * 2, it_total, clock64())
-                if (real && kDoPv) {
+                if (real) {
                   if (t == 0) issue_pv_stage<Cfg, Smem, 0>(sm, v_stage, i > 0 ? 1u : 0u);
                   else issue_pv_stage<Cfg, Smem, NT - 1>(sm, v_stage, i > 0 ? 1u : 0u);
                 }
@@ -1217,7 +1146,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                   umma_commit(&sm.s_full[t]);
                   // the QK just issued for the last tile is the item's last: Q may be overwritten after it
                   if (t == NT - 1 && i + 2 == count) umma_commit(&sm.q_empty);
-                } else if (real && kDoPv) {
+                } else if (real) {
                   umma_commit(&sm.o_final[t]);
                 }
                 MSA_TRACE(5 + t * 2, it_total, clock64())
@@ -1313,28 +1242,26 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 mbar_arrive(&sm.raw_empty[rs]);
               }
             }
-            if (kDoPv) {
-              const int rs = raw_seq % NRAW, st = v_seq % NV;
-              MSA_TBEGIN
-              ok = mbar_wait(&sm.raw_full[rs], (raw_seq / NRAW) & 1, abort_flag);
-              MSA_TEND(7)
-              MSA_TBEGIN
-              if (ok) ok = mbar_wait(&sm.v_empty[st], ((v_seq / NV) & 1) ^ 1, abort_flag);
-              MSA_TEND(8)
-              if (!ok) break;
-              ++raw_seq;
-              ++v_seq;
-              MSA_TBEGIN
-              convert(sm.raw[rs], sm.v[st] + dst_off);
-              fence_proxy_async();
-              __syncwarp();
-              if (lane == 0) {
-                mbar_arrive(&sm.v_full[st]);
-                mbar_arrive(&sm.raw_empty[rs]);
-              }
-              MSA_TEND(9)
+            const int rs = raw_seq % NRAW, st = v_seq % NV;
+            MSA_TBEGIN
+            ok = mbar_wait(&sm.raw_full[rs], (raw_seq / NRAW) & 1, abort_flag);
+            MSA_TEND(7)
+            MSA_TBEGIN
+            if (ok) ok = mbar_wait(&sm.v_empty[st], ((v_seq / NV) & 1) ^ 1, abort_flag);
+            MSA_TEND(8)
+            if (!ok) break;
+            ++raw_seq;
+            ++v_seq;
+            MSA_TBEGIN
+            convert(sm.raw[rs], sm.v[st] + dst_off);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+              mbar_arrive(&sm.v_full[st]);
+              mbar_arrive(&sm.raw_empty[rs]);
             }
-          }
+            MSA_TEND(9)
+                      }
           if (sparse) {
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.bm_empty[b]);
