@@ -709,6 +709,7 @@ def main():
     ap.add_argument("--stage", default="prefill", choices=["prefill", "decode", "topk", "proxy", "kvappend", "reference_sm100", "fp4_indexer"],
                     help="profiling runs: time only this stage and print a short JSON line")
     ap.add_argument("--no-ref", action="store_true", help="--stage fp4_indexer: skip the reference's kernel")
+    ap.add_argument("--fp4-case", default="", help="--stage fp4_indexer: only this case, e.g. prefill_q8k_k8k:nvfp4")
     ap.add_argument("--ref-kv", default="both", choices=["both", "fp8", "nvfp4"],
                     help="--stage reference_sm100: which K/V format to run")
     ap.add_argument("--decode-batch", type=int, default=32, help="requests of the decode case (131072-token contexts)")
@@ -776,6 +777,8 @@ def main():
         out = {"stage": "fp4_indexer", "cases": []}
         for case in FP4_CASES:
             for fmt in ("nvfp4", "mxfp4"):
+                if args.fp4_case and args.fp4_case != f"{case}:{fmt}":
+                    continue
                 try:
                     out["cases"].append(fp4_indexer_stage(dev, fmt, case, have_ref and not args.no_ref))
                 except Exception as e:  # noqa: BLE001
