@@ -147,7 +147,8 @@ typedef struct msa_fmha_args {
   void* out;              /* bf16 [total_q, num_qo_heads, 128], or NULL for the score-only pass */
   float* lse;             /* float32 [total_q, num_qo_heads] natural-log LSE, or NULL */
   float* max_score;       /* float32 [num_qo_heads, max_k_tiles, total_q] raw q.k tile maxima, or NULL.
-                             Only tiles the kernel visits are written; the caller pre-fills -inf. */
+                             Only tiles the kernel visits are written; the caller pre-fills -inf (or, for the
+                             score-only pass, sets score_fill_tail). */
   const int32_t* work;    /* int32 [n_work, 8], one entry per 128-row query tile, heaviest first:
                              {request, first token (global), valid rows <= 128 | first page << 10,
                               first token (request-local),
@@ -204,6 +205,13 @@ typedef struct msa_fmha_args {
                                     to 256 / hb tokens (msa_plan_desc.tile_rows = 256 / hb = msa_fmha_args.tile_rows).
                                     An entry may also cover only the pages from `first page` up (work[2] >> 10, as
                                     msa_plan_desc.dense_kv_splits writes it): per-page maxima need no merging */
+  int32_t score_fill_tail;       /* score-only pass: non-zero = work entries whose last field (work[7]) is 1 also write
+                                    -inf into max_score for the tiles above their own page range, up to max_k_tiles,
+                                    so the caller need not pre-fill the tensor.  Flag exactly one entry per (request,
+                                    query tile) -- the one that covers the highest pages when the page range is split
+                                    -- and keep the pre-fill if some query tile sees no page at all (it has no entry
+                                    that runs). */
+  int32_t reserved1;
   int64_t out_rows;              /* rows of out / lse; 0 = total_q.  dense_kv_splits * total_q when the work list
                                     was planned with KV splits: out and lse are then the partial buffers that
                                     msa_fmha_combine merges (lse must be given) */

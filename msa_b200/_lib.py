@@ -43,7 +43,7 @@ class FmhaArgs(Structure):
         ("sm_scale", c_float), ("qk_scale", c_float), ("v_scale", c_float),
         ("status", c_void_p), ("max_ctas", c_int32), ("qk_dim", c_int32),
         ("tile_rows", c_int32), ("tile_uniform", c_void_p), ("max_score_tile_stride", c_int64), ("max_score_head_stride", c_int64),
-        ("k_scale_format", c_int32), ("score_pack_heads", c_int32), ("out_rows", c_int64),
+        ("k_scale_format", c_int32), ("score_pack_heads", c_int32), ("score_fill_tail", c_int32), ("reserved1", c_int32), ("out_rows", c_int64),
     ]
 
 

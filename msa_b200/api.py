@@ -92,6 +92,30 @@ def _host_plan(qo_lens, kv_lens, qo_offset, causal: bool, paged: bool, num_qo_he
     return work, indptr, tok_req, tok_pos, int(splits.value)
 
 
+def _flag_fill_entries(work: np.ndarray, causal: bool) -> bool:
+    """Score-only work list: sets field 7 to 1 on the entry of every (request, query tile) that covers the tile's
+    highest pages -- the one that also writes -inf above them (``msa_fmha_args.score_fill_tail``) -- and 0 on the
+    others.  Returns False when some query tile sees no page at all: it has no entry that runs, so the caller has
+    to pre-fill the score tensor after all."""
+    if work.shape[0] == 0:
+        return True
+    rows, lo = work[:, 2] & 1023, work[:, 2] >> 10
+    vis = work[:, 4].astype(np.int64)
+    if causal:
+        vis = np.minimum(vis, work[:, 3].astype(np.int64) + rows + work[:, 5])
+    n_pages = np.where(vis > 0, (vis + PAGE - 1) // PAGE, 0)
+    walk = np.maximum(0, n_pages - lo)
+    work[:, 7] = 0
+    best = {}
+    for i in np.nonzero(walk > 0)[0].tolist():
+        key = (int(work[i, 0]), int(work[i, 1]))
+        if key not in best or lo[i] > lo[best[key]]:
+            best[key] = i
+    work[list(best.values()), 7] = 1
+    tiles = {(int(r[0]), int(r[1])) for r in work}
+    return len(best) == len(tiles)
+
+
 def build_work_list(qo_lens, kv_lens, qo_offset, causal: bool, paged: bool = True) -> np.ndarray:
     """One entry of 8 int32 per 128-row query tile: (request, first token (global),
     valid rows, first token (request-local), kv_len, causal offset, first page-table
@@ -207,6 +231,8 @@ def _fmha_sm100_plan(
     if output_maxscore and not sparse:
         # the score-only pass takes two query tiles per work item (every K page is fetched once for both)
         work2 = _host_plan(qo_lens, kv_lens, off, causal, page_size > 0, num_qo_heads, num_kv_heads, tile_rows=256)[0]
+        # the kernel writes -inf above every tile's pages itself, unless some tile has no page to visit
+        plan["score_fill"] = _flag_fill_entries(work2, causal)
         plan["work_score"] = torch.from_numpy(work2).to(device).contiguous()
     plan["status"] = torch.zeros(1, dtype=torch.int32, device=device)
     plan["use_decode_kernel"] = bool(use_decode)
@@ -309,7 +335,7 @@ def _kv_dtype_code(k: torch.Tensor) -> int:
 
 
 def _run_prefill(q, k, v, plan, kv_indices, kv_block_indexes, qo_offset_t, out, max_score, lse,
-                 sm_scale, qk_scale, v_scale, kv_dtype, is_paged, k_sf=None, v_sf=None, qk_dim=0):
+                 sm_scale, qk_scale, v_scale, kv_dtype, is_paged, k_sf=None, v_sf=None, qk_dim=0, fill_tail=False):
     lib = get_lib()
     a = FmhaArgs()
     a.qk_dim = int(qk_dim)
@@ -339,6 +365,7 @@ def _run_prefill(q, k, v, plan, kv_indices, kv_block_indexes, qo_offset_t, out, 
         raise MsaError("the plan and the call disagree on paged vs ragged K/V (pass page_size to fmha_sm100_plan)")
     a.work, a.n_work = _ptr(work), int(work.shape[0])
     a.tile_rows = 256 if score_pairs else 128
+    a.score_fill_tail = 1 if (fill_tail and score_pairs) else 0
     a.kv_indices = _ptr(kv_indices)
     a.kv_block_indexes = _ptr(kv_block_indexes)
     a.k_scale_128x4, a.v_scale_128x4 = _ptr(k_sf), _ptr(v_sf)
@@ -445,13 +472,17 @@ def _fmha_sm100(
     max_k_tiles = plan["max_k_tiles"]
     if kv_block_indexes is not None:
         output_maxscore = False          # the sparse pass has no max-score output (sparse_fmha_adapter.py:67-202)
+    fill_in_kernel = False
     if not output_maxscore or max_k_tiles == -1:
         max_score = None
         output_o = True
     elif max_score is None:
-        # untouched entries (beyond the causal frontier, padding tiles) must read -inf
-        max_score = torch.full((num_qo_heads, max_k_tiles, nnz_qo), -float("inf"), dtype=torch.float32,
-                               device=q.device)
+        # untouched entries (beyond the causal frontier, padding tiles) must read -inf: the score-only kernel writes
+        # them itself (no separate pass over the tensor); the attention kernel's Full mode needs the pre-fill
+        fill_in_kernel = (not output_o and kv_block_indexes is None and plan.get("score_fill", False)
+                          and q_offset_override is None and not plan["use_decode_kernel"] and nnz_qo > 0)
+        alloc = torch.empty if fill_in_kernel else (lambda *a, **k: torch.full(*a, -float("inf"), **k))
+        max_score = alloc((num_qo_heads, max_k_tiles, nnz_qo), dtype=torch.float32, device=q.device)
     if not output_o:
         out = None
     elif out is None:
@@ -497,7 +528,7 @@ def _fmha_sm100(
                 raise MsaError("score_dim=64 is for the score-only pass over bf16 or fp8 K")
             _run_prefill(q, k, v, plan, kv_indices, kv_block_indexes, qo_offset_t, out, max_score, lse,
                          sm_scale, q_scale * k_scale, v_scale * o_scale, kv_dtype, is_paged,
-                         qk_dim=0 if score_dim is None else score_dim)
+                         qk_dim=0 if score_dim is None else score_dim, fill_tail=fill_in_kernel)
     if return_lse:
         return out, max_score, lse
     return out, max_score

@@ -234,6 +234,7 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
   int nt = (p.hr % 2 == 0 && (!sparse || a->list_heads == a->num_kv_heads)) ? 2 : 1;
   if (score_only) nt = hb;  // the score kernel takes hb heads per work item
   p.pack_heads = hb;
+  p.fill_tail = score_only && a->score_fill_tail != 0;
   p.kv_pages = a->paged ? static_cast<int>(a->kv_rows < 0x7fffffffLL ? a->kv_rows : 0x7fffffffLL) : 0;
   p.n_head_groups = p.Hq / nt;
   const long long n_items = static_cast<long long>(p.n_work) * p.n_head_groups;

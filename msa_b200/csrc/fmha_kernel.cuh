@@ -78,6 +78,7 @@ struct FmhaParams {
                                  // values) or 512 (ue8m0 per 32 values, k_mx)
   int k_mx;
   int kv_pages;                  // paged K/V: physical pages in the pool (page-table entries are checked against it)
+  int fill_tail;                 // score kernel: entries flagged in work[7] write -inf above their page range
   int pack_heads;                // score-only pass: query heads per 128-row tile (a power of two dividing hr), else 1
   const uint8_t* k_raw;          // NVFP4 raw page storage
   const uint8_t* v_raw;

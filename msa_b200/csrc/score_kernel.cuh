@@ -91,7 +91,7 @@ constexpr int score_smem_bytes() {
 // covers the pages [page_lo, n_pages) from the top down; page_lo > 0 when the planner split the page range of an
 // entry over several work items (the per-page maxima of different pages are independent, so nothing is merged).
 struct ScoreItem {
-  int tok0, tokens, qloc0, h, g, kv_len, qo_off, kv_base, n_pages, n_walk, n_tiles;
+  int tok0, tokens, qloc0, h, g, kv_len, qo_off, kv_base, n_pages, n_walk, n_tiles, fill;
 };
 
 __device__ __forceinline__ ScoreItem score_item(const FmhaParams& p, int item) {
@@ -108,6 +108,7 @@ __device__ __forceinline__ ScoreItem score_item(const FmhaParams& p, int item) {
   it.kv_len = w2.x;
   it.qo_off = w2.y;
   it.kv_base = w2.z;
+  it.fill = w2.w;   // 1: this entry also writes -inf for the pages above its own, up to max_k_tiles
   it.n_tiles = it.tokens * p.pack_heads > 128 ? 2 : 1;
   int vis = it.kv_len;   // keys visible to the last token of the entry
   if (p.causal) vis = min(vis, it.qloc0 + it.tokens + it.qo_off);
@@ -427,6 +428,12 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         // waiting for it at the same pair cannot dead-lock: the ring holds at least two pairs.
         if (QB == 2 && pi == min(1, n_pairs - 1) && have_next) convert_q(n_q + 1, it_next.n_tiles);
       }
+      // the tiles nobody visits (beyond the causal frontier, beyond the request, padding up to max_k_tiles) read
+      // -inf: written by the kernel when the caller asks for it, so that no separate pass has to pre-fill the
+      // tensor -- here with packed e2m1 K, by the otherwise idle warp 11 in the other modes
+      if (Cfg::kKConvert && p.fill_tail != 0 && it.fill != 0 && mine && row_valid && ok) {
+        for (int pg = n; pg < p.max_k_tiles; ++pg) __stwt(dst + static_cast<long long>(pg) * p.ms_tile, -INFINITY);
+      }
       ++n_q;
       have = have_next;
       it = it_next;
@@ -592,6 +599,36 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       }
       MSA_TFLUSH(lane == 0 && me == 0, 4, 7)
       MSA_TFLUSH(lane == 0 && me == 0, 14, 15)
+    } else if (!Cfg::kKConvert && warp == Cfg::kCvtWarp0) {
+      // =======================================================================
+      // -inf for the tiles above every flagged entry's pages (score_fill_tail): this warp has no other work in the
+      // bf16 / e4m3 modes, so the stores overlap the MMAs instead of waiting at the end of every item
+      // =======================================================================
+      if (p.fill_tail != 0) {
+        int j = 0;
+        ScoreItem it;
+        while (next_item(j, it)) {
+          if (it.fill != 0) {
+            float* dst[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const int r_entry = e * 32 + lane;                  // rows of both tiles
+              const int tok_local = r_entry >> pack_shift;
+              const int head = it.h + (r_entry & (p.pack_heads - 1));
+              dst[e] = tok_local < it.tokens
+                           ? p.max_score + static_cast<long long>(head) * p.ms_head + it.tok0 + tok_local
+                           : nullptr;
+            }
+            for (int pg = it.n_pages; pg < p.max_k_tiles; ++pg) {
+              const long long off = static_cast<long long>(pg) * p.ms_tile;
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                if (dst[e] != nullptr) __stwt(dst[e] + off, -INFINITY);
+            }
+          }
+          ++j;
+        }
+      }
     } else if constexpr (Cfg::kKConvert) {
       // =======================================================================
       // dequantise raw e2m1 pages into f16 operand tiles (warps 11-15).  Block scales: e4m3 per 16 values (two

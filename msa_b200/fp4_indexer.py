@@ -18,7 +18,7 @@ import torch
 
 from . import _lib
 from ._lib import FmhaArgs, MsaError, check, get_lib
-from .api import _host_plan, _ptr, _stream
+from .api import _flag_fill_entries, _host_plan, _ptr, _stream
 
 PAGE = 128
 _GROUPS = {"mxfp4": 4, "nvfp4": 8}
@@ -153,8 +153,10 @@ def _plan(cu_q: torch.Tensor, cu_k: torch.Tensor, cu_p: torch.Tensor, qo_offset,
     if work.shape[0]:
         # page-table offsets as the caller gives them (they need not be the running sum of ceil(k_len / 128))
         work[:, 6] = [cp[r] for r in work[:, 0].tolist()]
-        work[:, 7] = 0
-    plan = dict(work=torch.from_numpy(work).to(cu_q.device).contiguous(), n_work=int(work.shape[0]), pack_heads=hb,
+    # the entry that covers a tile's highest pages also writes -inf above them (no pre-fill of the score tensor),
+    # unless some tile sees no page at all
+    fill = _flag_fill_entries(work, causal)
+    plan = dict(fill=fill, work=torch.from_numpy(work).to(cu_q.device).contiguous(), n_work=int(work.shape[0]), pack_heads=hb,
                 tile_rows=rows, status=torch.zeros(1, dtype=torch.int32, device=cu_q.device),
                 max_kv=max(kl) if kl else 0)
     if len(_PLAN_CACHE) > 64:
@@ -215,11 +217,14 @@ def fp4_indexer_block_scores(
         _check_mma_storage(q_scale, "q_scale", fmt, total_q, Hq)
         _check_mma_storage(k_scale, "k_scale", fmt, PAGE, n_pages * Hk)
     max_k_tiles = _ceil_div(int(max_seqlen_k), PAGE)
-    scores = torch.full((Hq, max_k_tiles, total_q), -float("inf"), dtype=torch.float32, device=q_fp4.device)
     if max_k_tiles == 0 or total_q == 0:
-        return scores
+        return torch.full((Hq, max_k_tiles, total_q), -float("inf"), dtype=torch.float32, device=q_fp4.device)
     lib = get_lib()
     plan = _plan(cu_seqlens_q, cu_seqlens_k, cu_page_offsets, qo_offset, bool(causal), Hq, Hk, int(max_seqlen_q))
+    if plan["fill"]:
+        scores = torch.empty((Hq, max_k_tiles, total_q), dtype=torch.float32, device=q_fp4.device)
+    else:
+        scores = torch.full((Hq, max_k_tiles, total_q), -float("inf"), dtype=torch.float32, device=q_fp4.device)
     if plan["max_kv"] > max_k_tiles * PAGE:
         raise ValueError("max_seqlen_k is smaller than the longest KV segment")
     # K scales: the kernel reads the tiled storage; logical ones are tiled first (what the reference does too)
@@ -239,6 +244,7 @@ def fp4_indexer_block_scores(
     a.out, a.lse, a.max_score = None, None, _ptr(scores)
     a.work, a.n_work, a.tile_rows = _ptr(plan["work"]), plan["n_work"], plan["tile_rows"]
     a.score_pack_heads = plan["pack_heads"]
+    a.score_fill_tail = 1 if plan["fill"] else 0
     a.kv_indices = _ptr(kv_indices.contiguous())
     a.k_scale_128x4 = _ptr(k_sf)
     a.k_scale_format = _FORMAT_CODE[fmt]

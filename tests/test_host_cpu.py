@@ -31,7 +31,7 @@ def test_library_exports_every_declared_symbol():
 
 def test_struct_layout_matches_header_sizes():
     # pointers 8 B, int64 8 B, int32/float 4 B: the ctypes mirror must not be smaller than the C struct
-    assert ctypes.sizeof(_lib.FmhaArgs) % 8 == 0 and ctypes.sizeof(_lib.FmhaArgs) == 224
+    assert ctypes.sizeof(_lib.FmhaArgs) % 8 == 0 and ctypes.sizeof(_lib.FmhaArgs) == 232
     assert ctypes.sizeof(_lib.DecodeArgs) == 144
 
 
