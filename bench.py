@@ -664,6 +664,45 @@ def cpu_sample_rate(seed, target_s=12.0, max_blocks=64):
     return flops / dt / 1e12, dt, n
 
 
+def cpu_reference_c1():
+    """BASELINE configuration 1 (1 x 4096 tokens, 8 / 1 heads, fp32 N(0,1), top-16 pages per 128-query block) through
+    the reference's OWN PyTorch code, `sparse_attention_ref` of python/fmha_sm100/cute/test_sparse_atten.py:201-365,
+    imported unmodified from the copy installed under baseline/_ref; all host threads.  None if the reference is not
+    installed on this box or fails to import."""
+    cute = os.path.join(ROOT, "baseline", "_ref", "fmha_sm100", "cute")
+    if not os.path.isfile(os.path.join(cute, "test_sparse_atten.py")):
+        return {"unavailable": "baseline/_ref/fmha_sm100/cute/test_sparse_atten.py is not installed on this box"}
+    try:
+        for pth in (os.path.join(ROOT, "baseline", "_ref"), cute):
+            if pth not in sys.path:
+                sys.path.insert(0, pth)
+        import test_sparse_atten as tsa           # the reference module, unmodified
+        torch.manual_seed(0)
+        S, hq, hkv, topk = 4096, 8, 1, 16
+        q = torch.randn(1, S, hq, D)
+        k = torch.randn(1, S, hkv, D)
+        v = torch.randn(1, S, hkv, D)
+        g = torch.Generator().manual_seed(0)
+        q2k = torch.full((1, hkv, S, topk), -1, dtype=torch.int32)
+        for blk in range(S // PAGE):
+            vis = blk + 1                            # causally visible pages of this 128-query block
+            ch = torch.randperm(vis, generator=g)[:topk].sort().values.int()
+            q2k[0, 0, blk * PAGE:(blk + 1) * PAGE, :ch.numel()] = ch
+        ts = []
+        for _ in range(3):
+            t0 = time.perf_counter()
+            tsa.sparse_attention_ref(q, k, v, q2k, causal=True)
+            ts.append(time.perf_counter() - t0)
+        dt = sorted(ts)[1]
+        flops = 8.0 * 4096 * 2048 * 512            # Hq * tokens * min(topk * 128, kv_len) * 512, the reference's count
+        return {"kind": "reference", "ms": dt * 1e3, "value": flops / dt / 1e12, "unit": "TFLOP/s",
+                "cores": torch.get_num_threads(),
+                "sample": "BASELINE config 1 (1 x 4096 tokens, 8/1 heads, fp32, top-16), the reference's "
+                          "sparse_attention_ref imported from baseline/_ref, median of 3"}
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"{type(e).__name__}: {str(e).splitlines()[0] if str(e) else ''}"[:200]}
+
+
 def run_reference_arm(args, rank):
     if rank != 0:
         return
@@ -997,6 +1036,9 @@ def main():
             line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
                                     "sample": f"last {n} 128-query blocks of the 16384-token request x {HQ} heads x "
                                               f"top-{TOPK} pages ({dt:.1f} s of CPU work), PyTorch CPU oracle"}
+            if world == 1:
+                # beside the port: the reference's own CPU function on its CPU-runnable configuration
+                line["cpu_baseline"]["reference_config1"] = cpu_reference_c1()
         if "e2e" not in line:
             line["e2e"] = None
         print(json.dumps(line), flush=True)
