@@ -282,3 +282,47 @@ def test_alias_package_exposes_the_reference_names():
     sig = inspect.signature(msa_b200.SparseDecodePagedAttentionWrapper.run)
     for kw in ("softmax_scale", "return_softmax_lse", "out", "lse"):
         assert kw in sig.parameters, kw
+
+
+def test_score_work_lists_tile_rows_splits_and_fill_flags():
+    """Work lists of the score-only pass: 256-row entries, 16-token entries for 16 packed heads, page-range splits,
+    and the entry of every query tile that is flagged to write the -inf tail."""
+    from msa_b200.api import _flag_fill_entries, _host_plan
+    w = _host_plan([600], [1000], None, True, True, 8, 8, tile_rows=256)[0]
+    assert sorted(r[2] for r in w.tolist()) == [88, 256, 256] and all(r[7] == 0 for r in w.tolist())
+    assert _flag_fill_entries(w, True) and all(r[7] == 1 for r in w.tolist())
+    # decode-like: 8 tokens per request in 16-token entries, three page ranges each
+    w = _host_plan([8, 8], [5000, 3000], None, True, True, 64, 4, tile_rows=16, dense_kv_splits=3)[0]
+    assert w.shape[0] == 6 and {r[2] & 1023 for r in w.tolist()} == {8}
+    assert _flag_fill_entries(w, True)
+    top = {}
+    for r in w.tolist():
+        top.setdefault(r[0], []).append((r[2] >> 10, r[7]))
+    for req, lst in top.items():
+        lst.sort()
+        assert [f for _, f in lst] == [0, 0, 1]          # only the highest page range writes the tail
+    # a query tile that sees no key at all (more queries than keys): no entry runs for it -> pre-fill needed
+    w = _host_plan([400], [100], None, True, True, 1, 1, tile_rows=256)[0]
+    assert not _flag_fill_entries(w, True)
+    # invalid sizes are refused by the planner
+    with pytest.raises(msa_b200.MsaError):
+        _host_plan([10], [10], None, True, True, 1, 1, tile_rows=512)
+
+
+def test_fp4_indexer_names_and_scale_layout_helpers():
+    """The FP4 indexer module and its alias import on a machine without a GPU; the storage helpers agree with the
+    oracle's offset formula (python/fmha_sm100/cute/fp4_indexer_interface.py:220-249)."""
+    import fmha_sm100.fp4_indexer_interface as fii
+    from oracle import msa_oracle as O
+    assert fii.fp4_indexer_block_scores is msa_b200.fp4_indexer_block_scores
+    for fmt, groups in (("nvfp4", 8), ("mxfp4", 4)):
+        mn, l = 300, 5
+        shape = fii.fp4_indexer_mma_scale_shape(mn, l, fp4_format=fmt)
+        stride = fii.fp4_indexer_mma_scale_stride(mn, l, fp4_format=fmt)
+        store = fii.fp4_indexer_mma_scale_storage_shape(mn, l, fp4_format=fmt)
+        assert shape == (32, 4, 3, 4, (groups + 3) // 4, l) and store == (l, 3, (groups + 3) // 4, 32, 4, 4)
+        for m, g, ll in ((0, 0, 0), (37, 3, 2), (299, groups - 1, 4), (128, 1, 1)):
+            idx = (m % 32, (m // 32) % 4, m // 128, g % 4, g // 4, ll)
+            assert sum(i * s_ for i, s_ in zip(idx, stride)) == O.fp4_mma_scale_offset(m, g, ll, mn, groups)
+    with pytest.raises(ValueError):
+        fii.fp4_indexer_mma_scale_shape(1, 1, fp4_format="fp4")
