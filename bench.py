@@ -665,7 +665,8 @@ def cpu_sample_rate(seed, target_s=12.0, max_blocks=64):
 
 
 def cpu_reference_c1():
-    """BASELINE configuration 1 (1 x 4096 tokens, 8 / 1 heads, fp32 N(0,1), top-16 pages per 128-query block) through
+    """The CPU-runnable configuration of the benchmark definition (1 x 4096 tokens, 8 / 1 heads, fp32 N(0,1), top-16
+    pages per 128-query block) through
     the reference's OWN PyTorch code, `sparse_attention_ref` of python/fmha_sm100/cute/test_sparse_atten.py:201-365,
     imported unmodified from the copy installed under baseline/_ref; all host threads.  None if the reference is not
     installed on this box or fails to import."""
@@ -697,7 +698,7 @@ def cpu_reference_c1():
         flops = 8.0 * 4096 * 2048 * 512            # Hq * tokens * min(topk * 128, kv_len) * 512, the reference's count
         return {"kind": "reference", "ms": dt * 1e3, "value": flops / dt / 1e12, "unit": "TFLOP/s",
                 "cores": torch.get_num_threads(),
-                "sample": "BASELINE config 1 (1 x 4096 tokens, 8/1 heads, fp32, top-16), the reference's "
+                "sample": "CPU-runnable configuration (1 x 4096 tokens, 8/1 heads, fp32, top-16), the reference's "
                           "sparse_attention_ref imported from baseline/_ref, median of 3"}
     except Exception as e:  # noqa: BLE001
         return {"unavailable": f"{type(e).__name__}: {str(e).splitlines()[0] if str(e) else ''}"[:200]}

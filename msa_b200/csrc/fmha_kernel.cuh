@@ -451,12 +451,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const int n_items_eff = (sm.abort == 0) ? p.n_items : 0;
   auto item_of = [&](int j) {
     const int base = j * static_cast<int>(gridDim.x);
-#ifdef MSA_NO_SNAKE
-    const int idx = base + static_cast<int>(blockIdx.x);
-#else
     const int idx = (j & 1) ? base + static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)
                             : base + static_cast<int>(blockIdx.x);
-#endif
     return (base < n_items_eff && idx < n_items_eff) ? idx : -1;
   };
 
@@ -823,7 +819,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         tc_fence_before();
         mbar_arrive(&sm.p_full[t]);
         if (r == 0) { MSA_TRACE(t * 2 + 1, it_total, clock64()) }
-                MSA_TEND(1)
+        MSA_TEND(1)
       }
       // this item's bitmap is no longer needed by my warp
       if (sparse) {
@@ -1262,7 +1258,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
               mbar_arrive(&sm.raw_empty[rs]);
             }
             MSA_TEND(9)
-                      }
+          }
           if (sparse) {
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.bm_empty[b]);
