@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import weakref
 from typing import Optional, Tuple, Union
 
 import numpy as np
@@ -90,6 +91,38 @@ def _host_plan(qo_lens, kv_lens, qo_offset, causal: bool, paged: bool, num_qo_he
     check(lib.msa_plan(ctypes.byref(d), _np_ptr(work), _np_ptr(indptr), _np_ptr(tok_req), _np_ptr(tok_pos),
                        ctypes.byref(splits)), "msa_plan")
     return work, indptr, tok_req, tok_pos, int(splits.value)
+
+
+class TensorKeyedCache:
+    """Host-side metadata derived from small device tensors (prefix sums, lengths), looked up by the identity and
+    version of those tensors so that only the first call with them pays the device-to-host read.  An entry is valid
+    only while the very same tensor objects are alive and unmodified: a new tensor that reuses the address of a
+    freed one (version 0 again, same shape) must not hit, so every entry keeps weak references and compares them."""
+
+    def __init__(self, max_entries: int = 32):
+        self._max = max_entries
+        self._entries: dict = {}
+
+    @staticmethod
+    def _key(tensors, extra):
+        return tuple(None if t is None else (t.data_ptr(), t._version, tuple(t.shape), str(t.device))
+                     for t in tensors) + tuple(extra)
+
+    def get(self, tensors, extra=()):
+        ent = self._entries.get(self._key(tensors, extra))
+        if ent is None:
+            return None
+        refs, value = ent
+        if all((r is None and t is None) or (r is not None and r() is t) for r, t in zip(refs, tensors)):
+            return value
+        return None
+
+    def put(self, tensors, extra, value):
+        if len(self._entries) >= self._max:
+            self._entries.pop(next(iter(self._entries)))
+        refs = tuple(None if t is None else weakref.ref(t) for t in tensors)
+        self._entries[self._key(tensors, extra)] = (refs, value)
+        return value
 
 
 def _flag_fill_entries(work: np.ndarray, causal: bool) -> bool:

@@ -18,13 +18,13 @@ import torch
 
 from . import _lib
 from ._lib import FmhaArgs, MsaError, check, get_lib
-from .api import _flag_fill_entries, _host_plan, _ptr, _stream
+from .api import TensorKeyedCache, _flag_fill_entries, _host_plan, _ptr, _stream
 
 PAGE = 128
 _GROUPS = {"mxfp4": 4, "nvfp4": 8}
 _FORMAT_CODE = {"nvfp4": 0, "mxfp4": 1}
 _PUBLIC, _MMA = "public", "preordered_mma"
-_PLAN_CACHE: dict = {}
+_PLAN_CACHE = TensorKeyedCache(64)
 
 
 def _fmt(fp4_format: str) -> str:
@@ -114,9 +114,8 @@ def _check_mma_storage(scale: torch.Tensor, name: str, fmt: str, mn: int, l: int
 def _plan(cu_q: torch.Tensor, cu_k: torch.Tensor, cu_p: torch.Tensor, qo_offset, causal: bool, Hq: int, Hk: int,
           max_q: int):
     """Work list of the score kernel for these prefix arrays (host copy once per distinct set of tensors)."""
-    key = tuple((t.data_ptr(), t._version, tuple(t.shape)) for t in (cu_q, cu_k, cu_p)) + (
-        None if qo_offset is None else (qo_offset.data_ptr(), qo_offset._version), bool(causal), Hq, Hk, int(max_q))
-    hit = _PLAN_CACHE.get(key)
+    key_tensors, key_extra = (cu_q, cu_k, cu_p, qo_offset), (bool(causal), Hq, Hk, int(max_q))
+    hit = _PLAN_CACHE.get(key_tensors, key_extra)
     if hit is not None:
         return hit
     cq, ck, cp = (t.detach().cpu().tolist() for t in (cu_q, cu_k, cu_p))
@@ -159,10 +158,7 @@ def _plan(cu_q: torch.Tensor, cu_k: torch.Tensor, cu_p: torch.Tensor, qo_offset,
     plan = dict(fill=fill, work=torch.from_numpy(work).to(cu_q.device).contiguous(), n_work=int(work.shape[0]), pack_heads=hb,
                 tile_rows=rows, status=torch.zeros(1, dtype=torch.int32, device=cu_q.device),
                 max_kv=max(kl) if kl else 0)
-    if len(_PLAN_CACHE) > 64:
-        _PLAN_CACHE.clear()
-    _PLAN_CACHE[key] = plan
-    return plan
+    return _PLAN_CACHE.put(key_tensors, key_extra, plan)
 
 
 def fp4_indexer_block_scores(

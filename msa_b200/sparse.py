@@ -20,7 +20,7 @@ import torch
 
 from . import _lib
 from ._lib import MsaError
-from .api import PAGE, _fmha_sm100_plan, _ptr, _run_decode, _run_prefill, _stream
+from .api import PAGE, TensorKeyedCache, _fmha_sm100_plan, _ptr, _run_decode, _run_prefill, _stream
 from .quant import Nvfp4QuantizedTensor  # noqa: F401  (re-export for callers of the nvfp4 entry point)
 
 
@@ -208,19 +208,14 @@ def k2q_csr_to_lists(k2q_row_ptr: torch.Tensor, k2q_q_indices: torch.Tensor, top
 # Host metadata of recent CSR calls, keyed by the identity and version of the length tensors: a model calls
 # the attention once per layer with the same cu_seqlens / seqused_k tensors, and only the first call of a
 # step has to read them back to the host and plan.
-_CSR_PLAN_CACHE: "dict[tuple, dict]" = {}
-_CSR_PLAN_CACHE_MAX = 16
-
-
-def _tensor_key(t):
-    return None if t is None else (t.data_ptr(), t._version, tuple(t.shape), str(t.device))
+_CSR_PLAN_CACHE = TensorKeyedCache(16)
 
 
 def _csr_plan(q, k, topK, cu_seqlens_q, cu_seqlens_k, blk_kv, causal, page_table, seqused_k):
     Hq, Hkv = q.shape[1], k.shape[1]
-    key = (_tensor_key(cu_seqlens_q), _tensor_key(cu_seqlens_k), _tensor_key(seqused_k), _tensor_key(page_table),
-           Hq, Hkv, topK, bool(causal), str(q.device))
-    hit = _CSR_PLAN_CACHE.get(key)
+    key_tensors = (cu_seqlens_q, cu_seqlens_k, seqused_k, page_table)
+    key_extra = (Hq, Hkv, topK, bool(causal), str(q.device))
+    hit = _CSR_PLAN_CACHE.get(key_tensors, key_extra)
     if hit is not None:
         return hit
     cq = [int(x) for x in cu_seqlens_q.tolist()]
@@ -247,10 +242,7 @@ def _csr_plan(q, k, topK, cu_seqlens_q, cu_seqlens_k, blk_kv, causal, page_table
         "kv_indices": _flat_page_table(page_table, kv_lens, blk_kv) if paged else None,
         "total_q": cq[-1],
     }
-    if len(_CSR_PLAN_CACHE) >= _CSR_PLAN_CACHE_MAX:
-        _CSR_PLAN_CACHE.pop(next(iter(_CSR_PLAN_CACHE)))
-    _CSR_PLAN_CACHE[key] = ent
-    return ent
+    return _CSR_PLAN_CACHE.put(key_tensors, key_extra, ent)
 
 
 def _csr_forward(q, k, v, k2q_row_ptr, k2q_q_indices, topK, cu_seqlens_q, cu_seqlens_k, blk_kv, causal,

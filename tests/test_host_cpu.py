@@ -326,3 +326,21 @@ def test_fp4_indexer_names_and_scale_layout_helpers():
             assert sum(i * s_ for i, s_ in zip(idx, stride)) == O.fp4_mma_scale_offset(m, g, ll, mn, groups)
     with pytest.raises(ValueError):
         fii.fp4_indexer_mma_scale_shape(1, 1, fp4_format="fp4")
+
+
+def test_plan_cache_does_not_survive_its_tensors():
+    """Plans cached per (cu_seqlens, ...) tensors: an in-place update misses, and so does another tensor object with
+    the same address, version and shape (what an allocator hands out after the original was freed)."""
+    from msa_b200.api import TensorKeyedCache
+    c = TensorKeyedCache(2)
+    a, b = torch.tensor([0, 5, 9]), torch.tensor([0, 7])
+    assert c.get((a, b, None), (1,)) is None
+    c.put((a, b, None), (1,), "plan1")
+    assert c.get((a, b, None), (1,)) == "plan1" and c.get((a, b, None), (2,)) is None
+    a.add_(1)
+    assert c.get((a, b, None), (1,)) is None
+    c.put((a, b, None), (1,), "plan2")
+    assert c.get((a.view_as(a), b, None), (1,)) is None      # same storage and version, different tensor object
+    c.put((b,), (), "x")
+    c.put((torch.tensor([1]),), (), "y")                      # capacity 2: the oldest entry is dropped
+    assert c.get((a, b, None), (1,)) is None
