@@ -405,7 +405,8 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             tmem_ld32p(s_cur + 160, c0 + 32);
           }
           fold(c1, limit_a - 64, vis_a, a0, a1, a2, a3);
-          if (row_valid)
+          // (a request longer than the score tensor's max_k_tiles pages is a caller error: its pages are not stored)
+          if (row_valid && page_a < p.max_k_tiles)
             __stwt(dst + static_cast<long long>(page_a) * p.ms_tile, fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) * row_scale);
           if (two) {
             tmem_ld32p(s_cur + 192, c1);
@@ -418,7 +419,7 @@ score_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             float b0 = -INFINITY, b1 = -INFINITY, b2 = -INFINITY, b3 = -INFINITY;
             fold(c0, limit_b, vis_b, b0, b1, b2, b3);
             fold(c1, limit_b - 64, vis_b, b0, b1, b2, b3);
-            if (row_valid)
+            if (row_valid && page_b < p.max_k_tiles)
               __stwt(dst + static_cast<long long>(page_b) * p.ms_tile, fmaxf(fmaxf(b0, b1), fmaxf(b2, b3)) * row_scale);
           }
           MSA_TEND(1)
