@@ -889,11 +889,13 @@ def main():
 
     line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": dict(workload_config(), lens=list(lens)),
+            "vs_baseline": None, "dtype": "e4m3", "data": "synthetic", "config": dict(workload_config(), lens=list(lens)),
             "gpu_launches": 2 * args.steps, "kernels_per_step": ["list_uniform_kernel", "fmha_fwd_kernel"],
             "kernel_status": status, "wall_ms_per_step": wall * 1e3 / args.steps,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak, "peak_kind": f"{peak_kind} burst bf16 (cuBLAS, best of 10)",
+                         "arithmetic": "Q.K and P.V are e4m3 x e4m3 -> f32 tcgen05 MMAs (Q as an e4m3 hi + lo pair); "
+                                       "the denominator is the measured 16-bit GEMM peak",
                          "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"],
                          "peak_sustained": peaks["bf16_tflops_sustained"],
                          "kernel": "fmha_fwd_kernel<2, KV_FP8, attention, page lists>", "launch_ms": kern_ms,

@@ -230,6 +230,20 @@ __device__ __forceinline__ void umma_ts_lohi(uint32_t d_tmem, uint32_t a_tmem, u
       "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// same with 8-bit operands (A: four e4m3 per TMEM column)
+__device__ __forceinline__ void umma_ts_f8_lohi(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t hi,
+                                                uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .b64 db;\n"
+      ".reg .pred p;\n"
+      "mov.b64 db, {%2, %3};\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], db, %4, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // low / high words of a 128-byte-swizzle shared-memory descriptor (see make_smem_desc)
 __device__ __forceinline__ uint32_t smem_desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
   return ((saddr & 0x3FFFFu) >> 4) | ((lbo_bytes >> 4) << 16);

@@ -254,7 +254,7 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
     const int fp8 = a->kv_dtype == MSA_KV_FP8_E4M3;
     rc = make_kv_map(&mk, a->k, a->kv_rows, p.Hkv, a->paged, fp8, 1, fp8 && score_only && p.half_dim);
     if (rc != MSA_OK) return rc;
-    rc = make_kv_map(&mv, a->v != nullptr ? a->v : a->k, a->kv_rows, p.Hkv, a->paged, fp8, 0);
+    rc = make_kv_map(&mv, a->v != nullptr ? a->v : a->k, a->kv_rows, p.Hkv, a->paged, fp8, MSA_FP8_PV);
     if (rc != MSA_OK) return rc;
   }
   if (score_only) {

@@ -8,17 +8,20 @@
 //   4*NT          producer: builds the page bitmap of the NEXT item while the current one computes,
 //                 prefetches its Q tile, and issues the TMA loads of the K/V pages named by the walk
 //   4*NT + 1      MMA issuer (one lane): S_t = Q_t K^T, O_t += P_t V with tcgen05, accumulators in TMEM
-//   4*NT + 2, +3  (quantised K/V) dequantise raw pages into f16 UMMA tiles
+//   4*NT + 2, +3  (NVFP4 K/V; FP8 V in the f16-P build) dequantise raw pages into f16 UMMA tiles
 // The last four warps form one warpgroup that gives registers back (setmaxnreg) to the softmax
 // warpgroups, which keep a whole 128-column S row in registers.
-// TMEM columns: S_t at t*128 (P_t aliases the first 64 columns of S_t), O_t at 256 + t*128.
+// TMEM columns: S_t at t*128 (P_t aliases the first 64 columns of S_t, the first 32 when P is e4m3),
+// O_t at 256 + t*128.
 // Pages are walked from the highest logical page down, so the causally masked tile comes first.
 //
 // K/V formats:
 //   bf16   K and V tiles come from TMA in the SW128 UMMA layout; bf16 x bf16 MMAs.
 //   e4m3   K pages go to the tensor core as stored (kind::f8f6f4) against Q split into two e4m3
-//          terms per row (q = s * (hi + lo), s a power of two), so only V is dequantised (to f16);
-//          P is f16.
+//          terms per row (q = s * (hi + lo), s a power of two).  V pages also feed the tensor core as
+//          stored, as the MN-major B operand of kind::f8f6f4 MMAs whose A operand is P rounded to e4m3 in
+//          TMEM; the row sum is taken from the unrounded f32 P.  (MSA_FP8_PV=0 builds: V dequantised to
+//          f16 by the convert warps, P in f16.)
 //   nvfp4  K and V are dequantised (e2m1 x e4m3 block scale, exact in f16); Q is converted to f16.
 #pragma once
 #include "common.cuh"
@@ -29,6 +32,7 @@ constexpr int kTileBytes = 128 * 128 * 2;  // one 128x128 16-bit operand tile
 constexpr int kHalfBytes = kTileBytes / 2;  // one 64-column SW128 sub-tile; also one 128x128 8-bit tile
 constexpr int kBitmapWords = 512;           // up to 16384 logical pages per request
 constexpr float kRescaleThreshold = 8.0f;   // lazy O rescale: tolerate row-max growth of 2^8
+constexpr float kRescaleThresholdE4 = 4.0f; // same when P is e4m3 (max 448): P is carried x2^4, so 2^4 more fits
 // P leaves the softmax as a truncated 16-bit float built with integer ops (the f32 -> 16-bit conversion
 // instruction shares a pipe with ex2, the unit this kernel saturates):
 //   bf16: keep the upper 16 bits of exp2(x + log2(1 + 2^-9)); the added factor centres the truncation error.
@@ -39,6 +43,22 @@ constexpr float kBiasBf16 = 0.0028150156f;             // log2(1 + 2^-9)
 constexpr float kGainBf16 = 1.001953125f;              // 1 + 2^-9
 constexpr float kBiasF16 = 0.00070426374f - 105.0f;    // log2(1 + 2^-11) - 105
 constexpr float kGainF16 = 1.00048828125f / 5.1922968585348276e33f;  // (1 + 2^-11) / 2^112
+//   e4m3: exp2(x - 116) has the e4m3 exponent field in place (f32 bias 127 = e4m3 bias 7 + 120, P carried
+//         x2^4: weights down to 2^-10 of the row maximum stay normal, smaller ones are dropped); bits >> 20,
+//         rounded to nearest, are the e4m3.  The gain
+//         2^-120 is applied in two halves so that no intermediate of the normalisation leaves the normal
+//         f32 range.
+constexpr float kBiasE4 = -116.0f;
+constexpr float kGainE4Num = 1.0f / 1.152921504606846976e18f;      // 2^-60
+constexpr float kGainE4Den = 1.152921504606846976e18f;             // 2^60
+#ifndef MSA_PV8_STAGES
+#define MSA_PV8_STAGES 2
+#endif
+// FP8 K/V calls multiply an e4m3 P by the V pages as stored (no V dequantisation, half the P.V tensor time).
+// Building with -DMSA_FP8_PV=0 keeps P in f16 and dequantises V to f16 instead: slower, P exact to 11 bits.
+#ifndef MSA_FP8_PV
+#define MSA_FP8_PV 1
+#endif
 
 enum KvMode : int { KV_BF16 = 0, KV_FP8 = 1, KV_NVFP4 = 2 };
 
@@ -96,12 +116,16 @@ struct FmhaCfg {
   static constexpr bool kQuant = KVMODE != KV_BF16;
   static constexpr bool kKDirectFp8 = KVMODE == KV_FP8;     // K pages feed kind::f8f6f4 MMAs as stored
   static constexpr bool kKConvert = KVMODE == KV_NVFP4;     // K is dequantised by the convert warps
-  static constexpr bool kVConvert = kQuant;                 // V is dequantised by the convert warps
+  static constexpr bool kPvFp8 = KVMODE == KV_FP8 && MSA_FP8_PV != 0;   // P.V in e4m3 on V pages as stored
+  static constexpr bool kVConvert = kQuant && !kPvFp8;      // V is dequantised by the convert warps
+  static constexpr bool kHasCvt = kKConvert || kVConvert;   // the convert warps have work
   static constexpr bool kQConvert = kQuant;                 // softmax threads rewrite Q (f16, or e4m3 hi/lo)
   static constexpr int kKBytes = kKDirectFp8 ? kHalfBytes : kTileBytes;
-  static constexpr int kKStages = 2;
-  static constexpr int kVStages = 2;
-  static constexpr int kRawStages = kQuant ? 2 : 0;
+  // ring depth: two stages each; e4m3 P.V has neither raw staging nor 16-bit V tiles and spends the space on depth
+  static constexpr int kKStages = kPvFp8 ? MSA_PV8_STAGES : 2;
+  static constexpr int kVStages = kPvFp8 ? MSA_PV8_STAGES : 2;
+  static constexpr int kVBytes = kPvFp8 ? kHalfBytes : kTileBytes;
+  static constexpr int kRawStages = kHasCvt ? 2 : 0;
   static constexpr int kRawBytes = KVMODE == KV_NVFP4 ? 10240 : 16384;
   static constexpr int kSoftmaxWarps = 4 * NT;
   // output through shared-memory staging + TMA stores; the two-head NVFP4 variant has no shared memory left
@@ -126,7 +150,7 @@ struct FmhaCfg {
   // UMMA operand format of the 16-bit MMAs (A and B must match): bf16 from TMA, f16 once K/V are dequantised
   static constexpr int kFmt16 = kQuant ? 0 : 1;
   // arrivals that release a bitmap buffer: one per softmax warp, the MMA warp, each convert warp
-  static constexpr int kBmEmptyCount = kSoftmaxWarps + 1 + (kQuant ? 2 : 0);
+  static constexpr int kBmEmptyCount = kSoftmaxWarps + 1 + (kHasCvt ? 2 : 0);
 };
 
 template <int NT, int KVMODE>
@@ -134,7 +158,7 @@ struct __align__(1024) FmhaSmem {
   using Cfg = FmhaCfg<NT, KVMODE>;
   uint8_t q[NT][kTileBytes];
   uint8_t k[Cfg::kKStages][Cfg::kKBytes];
-  uint8_t v[Cfg::kVStages][kTileBytes];
+  uint8_t v[Cfg::kVStages][Cfg::kVBytes];
   uint8_t raw[Cfg::kRawStages > 0 ? Cfg::kRawStages : 1][Cfg::kRawStages > 0 ? Cfg::kRawBytes : 16];
   // output staging, one 32-row x 32-column bf16 piece (64-byte rows, 64-byte swizzle) per softmax warp: the
   // epilogue writes its rows here and a TMA store moves them out, instead of 16-byte stores scattered over
@@ -351,12 +375,21 @@ template <class Cfg, class Smem, int T, int S>
 __device__ __forceinline__ void issue_pv_static(Smem& sm, uint32_t accumulate) {
   // B = V tile, MN-major: 16 keys per step = 2 KiB; d halves 16 KiB apart (LBO), 8-key groups 1 KiB apart (SBO)
   constexpr uint32_t desc_hi = smem_desc_hi(1024);
-  constexpr uint32_t idesc = make_idesc(128, 128, Cfg::kFmt16, Cfg::kFmt16, 0, 1);
   const uint32_t va = smem_desc_lo(smem_u32(sm.v[S]), kHalfBytes);
   constexpr uint32_t d = 256 + T * 128, a = T * 128;
-  umma_ts_lohi(d, a, va, desc_hi, idesc, accumulate);
+  if constexpr (Cfg::kPvFp8) {
+    // e4m3 P (four per TMEM column) x e4m3 V as stored: a 128-byte row holds all 128 d of one key, 32 keys
+    // per step = 4 KiB, 8-key groups 1 KiB apart (SBO); a single 128-byte block along d, so LBO is unused
+    constexpr uint32_t idesc8 = make_idesc(128, 128, 0, 0, 0, 1);
+    umma_ts_f8_lohi(d, a, va, desc_hi, idesc8, accumulate);
 #pragma unroll
-  for (int ks = 1; ks < 8; ++ks) umma_ts_lohi(d, a + ks * 8, va + ks * 128, desc_hi, idesc, 1u);
+    for (int ks = 1; ks < 4; ++ks) umma_ts_f8_lohi(d, a + ks * 8, va + ks * 256, desc_hi, idesc8, 1u);
+  } else {
+    constexpr uint32_t idesc = make_idesc(128, 128, Cfg::kFmt16, Cfg::kFmt16, 0, 1);
+    umma_ts_lohi(d, a, va, desc_hi, idesc, accumulate);
+#pragma unroll
+    for (int ks = 1; ks < 8; ++ks) umma_ts_lohi(d, a + ks * 8, va + ks * 128, desc_hi, idesc, 1u);
+  }
 }
 // same with the ring stage known at the call site, so that the addresses are constants plus the buffer base
 template <class Cfg, class Smem, int T, int S>
@@ -367,12 +400,19 @@ template <class Cfg, class Smem, int T>
 __device__ __forceinline__ void issue_qk_stage(Smem& sm, int stage) {
   if (stage == 0) issue_qk_static<Cfg, Smem, T, 0>(sm);
   else if (stage == 1) issue_qk_static<Cfg, Smem, T, 1>(sm);
-  else if constexpr (Cfg::kKStages > 2) issue_qk_static<Cfg, Smem, T, 2>(sm);
+  else if constexpr (Cfg::kKStages > 2) {
+    if (stage == 2) issue_qk_static<Cfg, Smem, T, 2>(sm);
+    else if constexpr (Cfg::kKStages > 3) issue_qk_static<Cfg, Smem, T, 3>(sm);
+  }
 }
 template <class Cfg, class Smem, int T>
 __device__ __forceinline__ void issue_pv_stage(Smem& sm, int stage, uint32_t accumulate) {
   if (stage == 0) issue_pv_static<Cfg, Smem, T, 0>(sm, accumulate);
-  else issue_pv_static<Cfg, Smem, T, 1>(sm, accumulate);
+  else if (stage == 1) issue_pv_static<Cfg, Smem, T, 1>(sm, accumulate);
+  else if constexpr (Cfg::kVStages > 2) {
+    if (stage == 2) issue_pv_static<Cfg, Smem, T, 2>(sm, accumulate);
+    else if constexpr (Cfg::kVStages > 3) issue_pv_static<Cfg, Smem, T, 3>(sm, accumulate);
+  }
 }
 
 // (The score-only pass, per-page max of Q K^T with no softmax and no V, is a kernel of its own: score_kernel.cuh.)
@@ -466,8 +506,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t s_addr = tmem + lane_base + t * 128;
     const uint32_t o_addr = tmem + lane_base + 256 + t * 128;
-    constexpr float kBias = Cfg::kQuant ? kBiasF16 : kBiasBf16;
-    constexpr float kGain = Cfg::kQuant ? kGainF16 : kGainBf16;
+    constexpr float kBias = Cfg::kPvFp8 ? kBiasE4 : Cfg::kQuant ? kBiasF16 : kBiasBf16;
+    constexpr float kGain = Cfg::kPvFp8 ? kGainE4Num : Cfg::kQuant ? kGainF16 : kGainBf16;
+    constexpr float kGainDen = Cfg::kPvFp8 ? kGainE4Den : 1.0f;
+    constexpr float kThreshold = Cfg::kPvFp8 ? kRescaleThresholdE4 : kRescaleThreshold;
     bool ok = true;
     uint32_t it_total = 0;   // S/P hand-overs so far (barrier phase)
     uint32_t n_q = 0;        // items with at least one page so far (q_full / q_ready phase)
@@ -637,7 +679,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
       }
       if (!ok) return;
-      const float inv = (pend.l_sum > 0.f) ? p.out_scale * kGain / pend.l_sum : 0.f;
+      const float inv = (pend.l_sum > 0.f) ? p.out_scale * kGain / (pend.l_sum * kGainDen) : 0.f;
       __nv_bfloat16* orow = p.out + (static_cast<size_t>(pend.tok) * p.Hq + pend.h) * 128;
       // a warp whose 32 rows all exist stages its piece in shared memory and lets TMA write it (rows of other
       // requests follow a partial tile in the output, so such a tile keeps the per-row stores)
@@ -772,7 +814,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 
         const float m_new = fmaxf(m_used, tmax);
         const bool first = (m_used == -INFINITY);
-        const bool need = !first && ((m_new - m_used) * sl2 > kRescaleThreshold);
+        const bool need = !first && ((m_new - m_used) * sl2 > kThreshold);
         if (__any_sync(0xffffffffu, need)) {
           // every MMA issued before the one that produced this S tile has completed, so O is quiescent;
           // eight columns at a time keeps the S row resident in registers
@@ -795,6 +837,32 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         // each S register dies as its exponential is taken
         const uint64_t sl2_2 = pack2(sl2, sl2), nmb_2 = pack2(kBias - mb, kBias - mb);
         uint64_t acc = 0ull;
+        if constexpr (Cfg::kPvFp8) {
+          // e4m3: four P per column, the first 32 columns of S
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t pk[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const int col = c * 32 + 4 * e;
+              float x0, x1, x2, x3;
+              unpack2(fma2(pack2u(sr[col], sr[col + 1]), sl2_2, nmb_2), x0, x1);
+              unpack2(fma2(pack2u(sr[col + 2], sr[col + 3]), sl2_2, nmb_2), x2, x3);
+              const float p0 = fast_exp2(x0), p1 = fast_exp2(x1), p2 = fast_exp2(x2), p3 = fast_exp2(x3);
+              const uint64_t p01 = pack2(p0, p1), p23 = pack2(p2, p3);
+              acc = add2(acc, p01);
+              acc = add2(acc, p23);
+              // f32 bits [26:20] are the e4m3; "<< 4, + half of the dropped part" rounds to nearest and leaves
+              // it in the top byte in one shift-add (the exponent field never passes 15, so nothing is cut off)
+              const uint32_t lo = __byte_perm((__float_as_uint(p0) << 4) + 0x800000u,
+                                              (__float_as_uint(p1) << 4) + 0x800000u, 0x0073);
+              const uint32_t hi = __byte_perm((__float_as_uint(p2) << 4) + 0x800000u,
+                                              (__float_as_uint(p3) << 4) + 0x800000u, 0x0073);
+              pk[e] = __byte_perm(lo, hi, 0x5410);
+            }
+            tmem_st8(s_addr + c * 8, pk);
+          }
+        } else {
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           uint32_t pk[8];
@@ -809,6 +877,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                                 : __byte_perm(__float_as_uint(p0), __float_as_uint(p1), 0x7632);
           }
           tmem_st8(s_addr + c * 8, pk);
+        }
         }
         {
           float a0, a1;
@@ -1034,8 +1103,13 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             ok = mbar_wait(&sm.v_empty[s], ((v_seq / NV) & 1) ^ 1, abort_flag);
             if (!ok) return;
             ++v_seq;
-            mbar_expect_tx(&sm.v_full[s], kTileBytes);
-            if (p.paged) {
+            mbar_expect_tx(&sm.v_full[s], Cfg::kPvFp8 ? kHalfBytes : kTileBytes);
+            if constexpr (Cfg::kPvFp8) {
+              if (p.paged)
+                tma_load_4d(sm.v[s], &tmap_v, &sm.v_full[s], 0, 0, info.g, phys);
+              else
+                tma_load_3d(sm.v[s], &tmap_v, &sm.v_full[s], 0, info.g, tok_k);
+            } else if (p.paged) {
               tma_load_4d(sm.v[s], &tmap_v, &sm.v_full[s], 0, 0, info.g, phys);
               tma_load_4d(sm.v[s] + kHalfBytes, &tmap_v, &sm.v_full[s], 64, 0, info.g, phys);
             } else {
@@ -1158,8 +1232,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       }
       MSA_TFLUSH(lane == 0, 3, 7)
       MSA_TFLUSH(lane == 0, 14, 15)
-    } else if (Cfg::kQuant && warp >= Cfg::kCvtWarp0) {
-      if constexpr (Cfg::kQuant) {
+    } else if (Cfg::kHasCvt && warp >= Cfg::kCvtWarp0) {
+      if constexpr (Cfg::kHasCvt) {
         // =====================================================================
         // dequantise raw pages into the f16 UMMA tiles (the SW128 image a 16-bit TMA load would leave).
         // 64 threads; a thread owns one 16-value column group of every 8th row, so every shared-memory
