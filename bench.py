@@ -949,6 +949,16 @@ def main():
             worst, n = sampled_output_check(w)
             oracle_check = {"max_abs_vs_oracle": worst, "blocks": n, "tolerance": 6e-2,
                             "what": "last 128-query block of every request + a middle block of the longest, all heads"}
+        # ---- the same launch with P kept in f16 and V dequantised to f16 (msa_fmha_args.fp8_p_f16) ----
+        p_f16 = None
+        if rank == 0:
+            with msa_b200.fp8_pv_precision("f16"):
+                mp, _ = time_fn(w["stage3"], 5, 2)
+                p_f16 = {"ms": mp, "tflops_effective": flops / (mp * 1e-3) / 1e12,
+                         "what": "the benchmark launch with msa_b200.fp8_pv_precision('f16'): P in f16, V dequantised "
+                                 "to f16 by two warps (the headline rounds P to e4m3 and multiplies V as stored)"}
+                if not args.no_cpu:
+                    p_f16["max_abs_vs_oracle"] = sampled_output_check(w)[0]
         keep = {k: w[k] for k in ("stage1", "stage2", "stage2_token", "lens", "ms")}
         del w
         w = keep
@@ -961,6 +971,8 @@ def main():
 
         # ---- the other stages, each timed alone (CUDA events, median) ------------
         stages = {}
+        if p_f16 is not None:
+            stages["sparse_prefill_fp8_p_f16"] = p_f16
         if c5_sharded is not None:
             stages["nvfp4_prefill_c5_sharded_by_kv_head"] = c5_sharded
         m1, _ = time_fn(w["stage1"], 3, 1)

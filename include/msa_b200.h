@@ -211,7 +211,10 @@ typedef struct msa_fmha_args {
                                     query tile) -- the one that covers the highest pages when the page range is split
                                     -- and keep the pre-fill if some query tile sees no page at all (it has no entry
                                     that runs). */
-  int32_t reserved1;
+  int32_t fp8_p_f16;             /* e4m3 K/V attention: 0 = P is rounded to e4m3 and multiplies the V pages as stored
+                                    (fastest; max-abs error vs fp32 ~1e-2 on outputs of magnitude 1); non-zero = V is
+                                    dequantised to f16 and P stays f16 (P exact to 11 bits, ~13 % slower).  Ignored
+                                    for other K/V formats and by the score-only pass */
   int64_t out_rows;              /* rows of out / lse; 0 = total_q.  dense_kv_splits * total_q when the work list
                                     was planned with KV splits: out and lse are then the partial buffers that
                                     msa_fmha_combine merges (lse must be given) */

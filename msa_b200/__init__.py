@@ -1,6 +1,7 @@
 """msa_b200: B200-native (sm_100a) kernels for the MSA block-sparse attention
 hot path behind the reference's Python API names."""
 from .api import (PlanInfo, fmha_sm100, fmha_sm100_plan, plan_status, sparse_topk_select)  # noqa: F401
+from .api import fp8_pv_precision, get_fp8_pv_precision, set_fp8_pv_precision  # noqa: F401
 from .quant import (Nvfp4QuantizedTensor, dequantize_nvfp4_128x4, quantize_bf16_to_nvfp4_128x4,  # noqa: F401
                     quantize_fp8_per_tensor, quantize_kv_bf16_to_nvfp4_128x4)
 from .sparse import (SparseDecodePagedAttentionWrapper, build_k2q_csr, k2q_csr_to_lists, k2q_csr_to_q2k,  # noqa: F401

@@ -22,7 +22,7 @@ SOURCES = ["abi.cu", "topk.cu", "decode.cu", "fmha_host.cu", "kv_quant.cu", "pla
 MSA_KV_BF16, MSA_KV_FP8_E4M3, MSA_KV_NVFP4 = 0, 1, 2
 MSA_ERR_TIMEOUT = -3
 MSA_ERR_BOUNDS = -6
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 
 class MsaError(RuntimeError):
@@ -43,7 +43,7 @@ class FmhaArgs(Structure):
         ("sm_scale", c_float), ("qk_scale", c_float), ("v_scale", c_float),
         ("status", c_void_p), ("max_ctas", c_int32), ("qk_dim", c_int32),
         ("tile_rows", c_int32), ("tile_uniform", c_void_p), ("max_score_tile_stride", c_int64), ("max_score_head_stride", c_int64),
-        ("k_scale_format", c_int32), ("score_pack_heads", c_int32), ("score_fill_tail", c_int32), ("reserved1", c_int32), ("out_rows", c_int64),
+        ("k_scale_format", c_int32), ("score_pack_heads", c_int32), ("score_fill_tail", c_int32), ("fp8_p_f16", c_int32), ("out_rows", c_int64),
     ]
 
 

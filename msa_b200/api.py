@@ -8,8 +8,10 @@ the sm_100a kernels only.  There is no CPU fallback.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import math
+import os
 import weakref
 from typing import Optional, Tuple, Union
 
@@ -35,6 +37,37 @@ def _ptr(t: Optional[torch.Tensor]):
 
 def _stream() -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+# Precision of P in attention over FP8 e4m3 K/V (msa_fmha_args.fp8_p_f16): "e4m3" multiplies a P rounded to e4m3
+# by the V pages as stored; "f16" dequantises V to f16 and keeps P in f16 (about 13 % slower, P exact to 11 bits).
+_FP8_PV_MODES = ("e4m3", "f16")
+_fp8_pv = os.environ.get("MSA_B200_FP8_PV", "e4m3")
+if _fp8_pv not in _FP8_PV_MODES:
+    raise ValueError(f"MSA_B200_FP8_PV must be one of {_FP8_PV_MODES}, got {_fp8_pv!r}")
+
+
+def set_fp8_pv_precision(mode: str) -> str:
+    """Chooses how attention over FP8 K/V computes P.V from now on ("e4m3" or "f16"); returns the former setting."""
+    global _fp8_pv
+    if mode not in _FP8_PV_MODES:
+        raise ValueError(f"mode must be one of {_FP8_PV_MODES}, got {mode!r}")
+    old, _fp8_pv = _fp8_pv, mode
+    return old
+
+
+def get_fp8_pv_precision() -> str:
+    return _fp8_pv
+
+
+@contextlib.contextmanager
+def fp8_pv_precision(mode: str):
+    """``with fp8_pv_precision("f16"): ...`` -- the setting of set_fp8_pv_precision for the calls inside."""
+    old = set_fp8_pv_precision(mode)
+    try:
+        yield
+    finally:
+        set_fp8_pv_precision(old)
 
 
 def _require_cuda(t: torch.Tensor, name: str):
@@ -399,6 +432,7 @@ def _run_prefill(q, k, v, plan, kv_indices, kv_block_indexes, qo_offset_t, out, 
     a.work, a.n_work = _ptr(work), int(work.shape[0])
     a.tile_rows = 256 if score_pairs else 128
     a.score_fill_tail = 1 if (fill_tail and score_pairs) else 0
+    a.fp8_p_f16 = 1 if _fp8_pv == "f16" else 0
     a.kv_indices = _ptr(kv_indices)
     a.kv_block_indexes = _ptr(kv_block_indexes)
     a.k_scale_128x4, a.v_scale_128x4 = _ptr(k_sf), _ptr(v_sf)

@@ -3,7 +3,7 @@
 
 extern "C" {
 
-int msa_abi_version(void) { return 3; }
+int msa_abi_version(void) { return 4; }
 
 const char* msa_error_string(int code) {
   switch (code) {

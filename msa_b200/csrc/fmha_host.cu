@@ -254,7 +254,7 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
     const int fp8 = a->kv_dtype == MSA_KV_FP8_E4M3;
     rc = make_kv_map(&mk, a->k, a->kv_rows, p.Hkv, a->paged, fp8, 1, fp8 && score_only && p.half_dim);
     if (rc != MSA_OK) return rc;
-    rc = make_kv_map(&mv, a->v != nullptr ? a->v : a->k, a->kv_rows, p.Hkv, a->paged, fp8, MSA_FP8_PV);
+    rc = make_kv_map(&mv, a->v != nullptr ? a->v : a->k, a->kv_rows, p.Hkv, a->paged, fp8, a->fp8_p_f16 == 0);
     if (rc != MSA_OK) return rc;
   }
   if (score_only) {
@@ -264,6 +264,10 @@ int fmha_fwd(const msa_fmha_args* a, cudaStream_t st) {
       case MSA_KV_NVFP4: return launch_score<KV_NVFP4>(mq, mk, p, a->max_ctas, st);
     }
     return MSA_ERR_UNSUPPORTED;
+  }
+  if (a->kv_dtype == MSA_KV_FP8_E4M3 && a->fp8_p_f16 != 0) {
+    if (nt == 1) return launch_fmha<1, KV_FP8_F16P>(mq, mk, mv, mo, p, a->max_ctas, st);
+    return launch_fmha<2, KV_FP8_F16P>(mq, mk, mv, mo, p, a->max_ctas, st);
   }
   switch (a->kv_dtype * 2 + (nt - 1)) {
     case 0: return launch_fmha<1, KV_BF16>(mq, mk, mv, mo, p, a->max_ctas, st);

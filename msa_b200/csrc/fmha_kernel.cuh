@@ -20,8 +20,9 @@
 //   e4m3   K pages go to the tensor core as stored (kind::f8f6f4) against Q split into two e4m3
 //          terms per row (q = s * (hi + lo), s a power of two).  V pages also feed the tensor core as
 //          stored, as the MN-major B operand of kind::f8f6f4 MMAs whose A operand is P rounded to e4m3 in
-//          TMEM; the row sum is taken from the unrounded f32 P.  (MSA_FP8_PV=0 builds: V dequantised to
-//          f16 by the convert warps, P in f16.)
+//          TMEM; the row sum is taken from the unrounded f32 P.
+//   e4m3 with f16 P (KV_FP8_F16P, chosen per call): K as above; V is dequantised to f16 by the convert warps
+//          and P stays f16 -- slower, P exact to 11 bits.
 //   nvfp4  K and V are dequantised (e2m1 x e4m3 block scale, exact in f16); Q is converted to f16.
 #pragma once
 #include "common.cuh"
@@ -54,13 +55,8 @@ constexpr float kGainE4Den = 1.152921504606846976e18f;             // 2^60
 #ifndef MSA_PV8_STAGES
 #define MSA_PV8_STAGES 2
 #endif
-// FP8 K/V calls multiply an e4m3 P by the V pages as stored (no V dequantisation, half the P.V tensor time).
-// Building with -DMSA_FP8_PV=0 keeps P in f16 and dequantises V to f16 instead: slower, P exact to 11 bits.
-#ifndef MSA_FP8_PV
-#define MSA_FP8_PV 1
-#endif
 
-enum KvMode : int { KV_BF16 = 0, KV_FP8 = 1, KV_NVFP4 = 2 };
+enum KvMode : int { KV_BF16 = 0, KV_FP8 = 1, KV_NVFP4 = 2, KV_FP8_F16P = 3 };
 
 // Optional per-role cycle accounting (build with -DMSA_ROLE_TIMING): lane 0 of one warp per role adds the
 // cycles it spent in each wait / work phase to a [n_cta][16] int64 buffer set through
@@ -114,9 +110,9 @@ struct FmhaParams {
 template <int NT, int KVMODE>
 struct FmhaCfg {
   static constexpr bool kQuant = KVMODE != KV_BF16;
-  static constexpr bool kKDirectFp8 = KVMODE == KV_FP8;     // K pages feed kind::f8f6f4 MMAs as stored
+  static constexpr bool kKDirectFp8 = KVMODE == KV_FP8 || KVMODE == KV_FP8_F16P;   // K pages feed kind::f8f6f4 MMAs as stored
   static constexpr bool kKConvert = KVMODE == KV_NVFP4;     // K is dequantised by the convert warps
-  static constexpr bool kPvFp8 = KVMODE == KV_FP8 && MSA_FP8_PV != 0;   // P.V in e4m3 on V pages as stored
+  static constexpr bool kPvFp8 = KVMODE == KV_FP8;          // P.V in e4m3 on the V pages as stored
   static constexpr bool kVConvert = kQuant && !kPvFp8;      // V is dequantised by the convert warps
   static constexpr bool kHasCvt = kKConvert || kVConvert;   // the convert warps have work
   static constexpr bool kQConvert = kQuant;                 // softmax threads rewrite Q (f16, or e4m3 hi/lo)
@@ -1087,7 +1083,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             ok = mbar_wait(&sm.raw_empty[s], ((raw_seq / NRAW) & 1) ^ 1, abort_flag);
             if (!ok) return;
             ++raw_seq;
-            if constexpr (KVMODE == KV_FP8) {
+            if constexpr (Cfg::kKDirectFp8) {
               mbar_expect_tx(&sm.raw_full[s], 16384);
               if (p.paged)
                 tma_load_4d(sm.raw[s], &tmap_v, &sm.raw_full[s], 0, 0, info.g, phys);
@@ -1246,7 +1242,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         bool ok = true;
         uint32_t raw_seq = 0, k_seq = 0, v_seq = 0;
         auto convert = [&](const uint8_t* rawp, uint8_t* dst) {
-          if constexpr (KVMODE == KV_FP8) {
+          if constexpr (Cfg::kKDirectFp8) {
             const uint8_t* src = rawp + ct * 16;   // row (it*8 + r8), bytes [c8*16, +16)
 #pragma unroll 4
             for (int it = 0; it < 16; ++it) {

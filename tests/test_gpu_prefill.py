@@ -99,6 +99,31 @@ def test_dense_full_mode(qo_lens, kv_lens, Hq, Hkv, kind):
     assert torch.allclose(got[fin], msref[fin], atol=2e-3 if kind == "bf16" else 1e-1, rtol=1e-3)
 
 
+@pytest.mark.parametrize("kind", ["bf16", "fp8"])
+def test_row_maximum_grows_on_every_page(kind):
+    """The walk runs from the last page down; here the scores of logical page j are about 4 * (7 - j) nats, so
+    every row's maximum grows by ~5.8 in log2 on each step, past the lazy-rescale threshold of either P format:
+    O is rescaled on every page and P must stay inside its number range (e4m3 tops out at 448)."""
+    kv_len, n_pages, Hq, Hkv = 1024, 8, 2, 1
+    g = torch.Generator().manual_seed(77)
+    w = torch.randn(128, generator=g)
+    q = (w[None, None, :] + 0.1 * torch.randn(128, Hq, 128, generator=g)).to(torch.bfloat16)
+    kp = 0.3 * torch.randn(n_pages, Hkv, 128, 128, generator=g)
+    vp = torch.randn(n_pages, Hkv, 128, 128, generator=g).to(torch.bfloat16)
+    table = torch.randperm(n_pages, generator=g).int()
+    for j in range(n_pages):
+        kp[table[j]] += 4.0 * (n_pages - 1 - j) * (128 ** 0.5) * w / w.pow(2).sum()
+    kp = kp.to(torch.bfloat16)
+    kd, vd, kr, vr, kw = _quantise(kp, vp, kind)
+    plan = msa_b200.fmha_sm100_plan(torch.tensor([128]), torch.tensor([kv_len]), Hq, num_kv_heads=Hkv, page_size=128)
+    out, _, lse = msa_b200.fmha_sm100(q.cuda(), kd, vd, plan, kv_indices=table.cuda(), return_lse=True, **kw)
+    assert msa_b200.plan_status(plan) == 0
+    ref, lse_ref = O.dense_attention_paged(q, kr, vr, table, [128], [kv_len])
+    assert bool(torch.isfinite(out.float()).all())
+    assert (out.float().cpu() - ref).abs().max() <= TOL[kind]
+    assert torch.allclose(lse.cpu(), lse_ref, atol=2e-2, rtol=1e-3)
+
+
 @pytest.mark.parametrize("qo_lens,kv_lens,Hq,Hkv,kind,splits,causal", [
     ([40, 3], [5000, 9000], 8, 2, "bf16", -1, True),       # planner's own choice (few tiles, long contexts)
     ([40, 3], [5000, 9000], 8, 2, "fp8", 3, True),
@@ -254,6 +279,42 @@ def test_sparse_prefill(qo_lens, kv_lens, Hq, Hkv, topk, kind, lists):
     assert torch.equal(torch.isfinite(lse.cpu()), torch.isfinite(lse_ref))
     fin = torch.isfinite(lse_ref)
     assert torch.allclose(lse.cpu()[fin], lse_ref[fin], atol=2e-2, rtol=1e-3)
+
+
+@pytest.mark.parametrize("lists,qo_lens,kv_lens,Hq,Hkv,topk", [
+    (None, [70, 128, 200], [300, 128, 457], 4, 2, 0),        # dense, ragged
+    ("block", [256, 33], [2048, 4000], 16, 2, 16),
+    ("token", [300, 100], [900, 1000], 6, 6, 4),             # one query head per CTA
+])
+def test_fp8_with_p_in_f16(lists, qo_lens, kv_lens, Hq, Hkv, topk):
+    """msa_fmha_args.fp8_p_f16 (msa_b200.fp8_pv_precision("f16")): V dequantised to f16, P kept in f16.  The error
+    against the fp32 oracle on the same dequantised K/V is that of the 16-bit paths, and the default (P rounded to
+    e4m3) stays within the FP8 tolerance on the same inputs."""
+    if lists is None:
+        kp, vp, table = make_paged(kv_lens, Hkv, 8)
+        q = torch.randn(sum(qo_lens), Hq, 128, generator=torch.Generator().manual_seed(9)).to(torch.bfloat16)
+        idx, plan_kw = None, {}
+    else:
+        q, kp, vp, table, idx = _sparse_case(qo_lens, kv_lens, Hq, Hkv, topk, "fp8", lists, seed=61)
+        plan_kw = dict(kv_block_num=topk, sparse_kernel_mode="prefill")
+    kd, vd, kr, vr, kw = _quantise(kp, vp, "fp8")
+    plan = msa_b200.fmha_sm100_plan(torch.tensor(qo_lens), torch.tensor(kv_lens), Hq, num_kv_heads=Hkv, page_size=128,
+                                    **plan_kw)
+    call_kw = dict(kv_indices=table.cuda(), **kw)
+    if idx is not None:
+        call_kw["kv_block_indexes"] = idx.cuda()
+        ref, _ = O.sparse_attention_paged(q, kr, vr, table, qo_lens, kv_lens, idx)
+    else:
+        ref, _ = O.dense_attention_paged(q, kr, vr, table, qo_lens, kv_lens)
+    assert msa_b200.get_fp8_pv_precision() == "e4m3"
+    out8, _ = msa_b200.fmha_sm100(q.cuda(), kd, vd, plan, **call_kw)
+    with msa_b200.fp8_pv_precision("f16"):
+        out16, _ = msa_b200.fmha_sm100(q.cuda(), kd, vd, plan, **call_kw)
+    assert msa_b200.get_fp8_pv_precision() == "e4m3" and msa_b200.plan_status(plan) == 0
+    e8 = (out8.float().cpu() - ref).abs().max()
+    e16 = (out16.float().cpu() - ref).abs().max()
+    assert e16 <= TOL["bf16"] and e8 <= TOL["fp8"]
+    assert e16 <= e8 + 4e-3          # bf16 output rounding is common to both
 
 
 def test_sparse_per_query_head_lists():

@@ -25,7 +25,7 @@ def test_library_exports_every_declared_symbol():
     lib = msa_b200.get_lib()
     for n in sorted(names):
         assert hasattr(lib, n), f"{n} declared in the header but not exported"
-    assert lib.msa_abi_version() == 3
+    assert lib.msa_abi_version() == 4
     assert lib.msa_error_string(-3).decode().startswith("device-side wait")
 
 
