@@ -839,13 +839,12 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
               const uint64_t p01 = pack2(p0, p1), p23 = pack2(p2, p3);
               acc = add2(acc, p01);
               acc = add2(acc, p23);
-              // f32 bits [26:20] are the e4m3; "<< 4, + half of the dropped part" rounds to nearest and leaves
-              // it in the top byte in one shift-add (the exponent field never passes 15, so nothing is cut off)
-              const uint32_t lo = __byte_perm((__float_as_uint(p0) << 4) + 0x800000u,
-                                              (__float_as_uint(p1) << 4) + 0x800000u, 0x0073);
-              const uint32_t hi = __byte_perm((__float_as_uint(p2) << 4) + 0x800000u,
-                                              (__float_as_uint(p3) << 4) + 0x800000u, 0x0073);
-              pk[e] = __byte_perm(lo, hi, 0x5410);
+              // f32 bits [26:20] are the e4m3.  The upper halves of two values are packed into one word first
+              // (bits [10:4] of each half); one shift-add then rounds both to nearest and leaves them in bytes 1
+              // and 3 (the exponent field never passes 15, so nothing crosses from the lower half into the upper)
+              const uint32_t lo = (__byte_perm(__float_as_uint(p0), __float_as_uint(p1), 0x7632) << 4) + 0x00800080u;
+              const uint32_t hi = (__byte_perm(__float_as_uint(p2), __float_as_uint(p3), 0x7632) << 4) + 0x00800080u;
+              pk[e] = __byte_perm(lo, hi, 0x7531);
             }
             tmem_st8(s_addr + c * 8, pk);
           }
