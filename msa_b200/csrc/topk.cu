@@ -428,14 +428,28 @@ topk_select_fast_kernel(const __grid_constant__ CUtensorMap tmap_ms, int H, int 
   for (int j = 0; j < GPT; ++j) gm[j] = -INFINITY;
   const int n_i = max(0, min(64, (keff - u + 15) >> 4));   // my pages: u + 16 i, i < n_i
   const float* col = &sm.slab[u][t];                       // page u + 16 i sits 16 * kFastTok floats further on
-  // eight loads in flight per step: the loop is bound by shared-memory latency, not by instruction count
-  for (int i0 = 0; i0 < 64; i0 += 8) {
-    if (i0 == 32 && !forced_any && ok) ok = mbar_wait(&sm.full[1], 0, abort_flag);   // pages from 512 on
-    float v[8];
+  // eight loads in flight per step: the loop is bound by shared-memory latency, not by instruction count.
+  // A full row (1024 pages: every thread owns 64) takes the loop without the per-element bound checks.
+  const bool full_row = keff == kTopkChunk;   // CTA-uniform
+  if (full_row) {
 #pragma unroll
-    for (int e = 0; e < 8; ++e) v[e] = (i0 + e < n_i) ? col[(i0 + e) * 16 * kFastTok] : -INFINITY;
+    for (int i0 = 0; i0 < 64; i0 += 8) {
+      if (i0 == 32 && !forced_any && ok) ok = mbar_wait(&sm.full[1], 0, abort_flag);   // pages from 512 on
+      float v[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) gm[(i0 + e) % GPT] = fmaxf(gm[(i0 + e) % GPT], v[e]);   // NaN never wins
+      for (int e = 0; e < 8; ++e) v[e] = col[(i0 + e) * 16 * kFastTok];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) gm[(i0 + e) % GPT] = fmaxf(gm[(i0 + e) % GPT], v[e]);   // NaN never wins
+    }
+  } else {
+    for (int i0 = 0; i0 < 64; i0 += 8) {
+      if (i0 == 32 && !forced_any && ok) ok = mbar_wait(&sm.full[1], 0, abort_flag);   // pages from 512 on
+      float v[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = (i0 + e < n_i) ? col[(i0 + e) * 16 * kFastTok] : -INFINITY;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) gm[(i0 + e) % GPT] = fmaxf(gm[(i0 + e) % GPT], v[e]);   // NaN never wins
+    }
   }
   bool saw_inf = false;
 #pragma unroll
@@ -466,25 +480,60 @@ topk_select_fast_kernel(const __grid_constant__ CUtensorMap tmap_ms, int H, int 
   // ---- B: candidates ------------------------------------------------------------------------------------------
   {
     const float thr = sm.thr[t];
-    for (int i0 = 0; i0 < n_i; i0 += 8) {
-      float v[8];
+    // which of my 64 scores are candidates; slots are then reserved with one shared-memory atomic per pair of
+    // threads (lanes l and l ^ 16 serve the same row) instead of one per candidate
+    uint32_t m0 = 0u, m1 = 0u;
+    // v >= thr && v > -inf  <=>  v >= max(thr, -FLT_MAX); NaN fails the comparison
+    const float lower = fmaxf(thr, -3.402823466e38f);
+    if (full_row) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) v[e] = (i0 + e < n_i) ? col[(i0 + e) * 16 * kFastTok] : -INFINITY;
-      bool any = false;
+      for (int i0 = 0; i0 < 64; i0 += 8) {
+        float v[8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) any |= (v[e] >= thr && v[e] > -INFINITY);
-      if (any) {
+        for (int e = 0; e < 8; ++e) v[e] = col[(i0 + e) * 16 * kFastTok];
+        uint32_t bits = 0u;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          if (v[e] >= thr && v[e] > -INFINITY) {
-            const int slot = atomicAdd(&sm.cnt[t], 1);
-            if (slot < C) {
-              sm.cand_v[t][slot] = v[e] + 0.0f;   // -0.0 -> +0.0
-              sm.cand_k[t][slot] = static_cast<short>(u + 16 * (i0 + e));
-            }
-          }
+        for (int e = 0; e < 8; ++e) bits |= (v[e] >= lower) ? (1u << e) : 0u;
+        if (i0 < 32) m0 |= bits << (i0 & 31);
+        else m1 |= bits << (i0 & 31);
+      }
+    } else {
+#pragma unroll
+      for (int i0 = 0; i0 < 64; i0 += 8) {
+        if (i0 < n_i) {
+          float v[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] = (i0 + e < n_i) ? col[(i0 + e) * 16 * kFastTok] : -INFINITY;
+          uint32_t bits = 0u;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) bits |= (v[e] >= lower) ? (1u << e) : 0u;
+          if (i0 < 32) m0 |= bits << (i0 & 31);
+          else m1 |= bits << (i0 & 31);
         }
       }
+    }
+    const int mine = __popc(m0) + __popc(m1);
+    const int pair = __shfl_xor_sync(0xffffffffu, mine, 16);
+    int slot = 0;
+    if (lane < 16 && mine + pair > 0) slot = atomicAdd(&sm.cnt[t], mine + pair);
+    slot = __shfl_sync(0xffffffffu, slot, lane & 15) + (lane >= 16 ? pair : 0);
+    while (m0 != 0u) {
+      const int i = __ffs(m0) - 1;
+      m0 &= m0 - 1;
+      if (slot < C) {
+        sm.cand_v[t][slot] = col[i * 16 * kFastTok] + 0.0f;   // -0.0 -> +0.0
+        sm.cand_k[t][slot] = static_cast<short>(u + 16 * i);
+      }
+      ++slot;
+    }
+    while (m1 != 0u) {
+      const int i = 32 + __ffs(m1) - 1;
+      m1 &= m1 - 1;
+      if (slot < C) {
+        sm.cand_v[t][slot] = col[i * 16 * kFastTok] + 0.0f;
+        sm.cand_k[t][slot] = static_cast<short>(u + 16 * i);
+      }
+      ++slot;
     }
   }
   __syncthreads();
@@ -497,6 +546,76 @@ topk_select_fast_kernel(const __grid_constant__ CUtensorMap tmap_ms, int H, int 
     int* o = out + (static_cast<size_t>(tok) * H + h) * TOPK;
     const int n = sm.cnt[row];
     int n_sel = 0;
+    if (n <= 32) {
+      // the usual case, one candidate per lane: rank and output position from register shuffles alone
+      const float va = lane < n ? sm.cand_v[row][lane] : 0.f;
+      const int ka = lane < n ? sm.cand_k[row][lane] : 0;
+      int rank = 0;
+#pragma unroll 4
+      for (int b = 0; b < n; ++b) {        // n is warp-uniform
+        const float vb = __shfl_sync(0xffffffffu, va, b);
+        const int kb = __shfl_sync(0xffffffffu, ka, b);
+        rank += (vb > va || (vb == va && kb < ka)) ? 1 : 0;
+      }
+      const bool keep = lane < n && rank < TOPK;
+      uint32_t m = __ballot_sync(0xffffffffu, keep);
+      n_sel = __popc(m);
+      int pos = 0;                         // ascending page order: kept pages below mine
+      while (m != 0u) {
+        const int src = __ffs(m) - 1;
+        m &= m - 1;
+        pos += (__shfl_sync(0xffffffffu, ka, src) < ka) ? 1 : 0;
+      }
+      if (keep) o[pos] = ka;
+      for (int a = lane; a < TOPK; a += 32)
+        if (a >= n_sel) o[a] = -1;
+      continue;
+    }
+    if (n <= 64) {
+      // two candidates per lane (slots lane and lane + 32), same method
+      const int n0 = min(n, 32);
+      const float va0 = lane < n ? sm.cand_v[row][lane] : 0.f;
+      const int ka0 = lane < n ? sm.cand_k[row][lane] : 0;
+      const float va1 = lane + 32 < n ? sm.cand_v[row][lane + 32] : 0.f;
+      const int ka1 = lane + 32 < n ? sm.cand_k[row][lane + 32] : 0;
+      int rank0 = 0, rank1 = 0;
+#pragma unroll 4
+      for (int b = 0; b < n0; ++b) {        // n is warp-uniform
+        const float vb = __shfl_sync(0xffffffffu, va0, b);
+        const int kb = __shfl_sync(0xffffffffu, ka0, b);
+        rank0 += (vb > va0 || (vb == va0 && kb < ka0)) ? 1 : 0;
+        rank1 += (vb > va1 || (vb == va1 && kb < ka1)) ? 1 : 0;
+      }
+      for (int b = 32; b < n; ++b) {
+        const float vb = __shfl_sync(0xffffffffu, va1, b - 32);
+        const int kb = __shfl_sync(0xffffffffu, ka1, b - 32);
+        rank0 += (vb > va0 || (vb == va0 && kb < ka0)) ? 1 : 0;
+        rank1 += (vb > va1 || (vb == va1 && kb < ka1)) ? 1 : 0;
+      }
+      const bool keep0 = lane < n && rank0 < TOPK, keep1 = lane + 32 < n && rank1 < TOPK;
+      uint32_t m0 = __ballot_sync(0xffffffffu, keep0), m1 = __ballot_sync(0xffffffffu, keep1);
+      n_sel = __popc(m0) + __popc(m1);
+      int pos0 = 0, pos1 = 0;               // ascending page order: kept pages below mine
+      while (m0 != 0u) {
+        const int src = __ffs(m0) - 1;
+        m0 &= m0 - 1;
+        const int kb = __shfl_sync(0xffffffffu, ka0, src);
+        pos0 += (kb < ka0) ? 1 : 0;
+        pos1 += (kb < ka1) ? 1 : 0;
+      }
+      while (m1 != 0u) {
+        const int src = __ffs(m1) - 1;
+        m1 &= m1 - 1;
+        const int kb = __shfl_sync(0xffffffffu, ka1, src);
+        pos0 += (kb < ka0) ? 1 : 0;
+        pos1 += (kb < ka1) ? 1 : 0;
+      }
+      if (keep0) o[pos0] = ka0;
+      if (keep1) o[pos1] = ka1;
+      for (int a = lane; a < TOPK; a += 32)
+        if (a >= n_sel) o[a] = -1;
+      continue;
+    }
     if (n <= C) {
       // every lane owns candidates lane, lane + 32, ...; rank = number of candidates that beat it
       for (int a0 = 0; a0 < n; a0 += 32) {
