@@ -547,26 +547,48 @@ topk_select_fast_kernel(const __grid_constant__ CUtensorMap tmap_ms, int H, int 
     const int n = sm.cnt[row];
     int n_sel = 0;
     if (n <= 32) {
-      // the usual case, one candidate per lane: rank and output position from register shuffles alone
+      // The usual case, one candidate per lane, everything from registers: rank = candidates with a greater
+      // score (one shuffle and one compare each); equal scores, rare, are ordered by page in a second loop that
+      // runs only if some lanes hold the same score.  The kept pages leave in ascending order through a
+      // 1024-bit map (the row's candidate buffer, free once the candidates are in registers): lane L owns pages
+      // 32 L .. 32 L + 31, a prefix sum of the population counts gives its first output slot.
       const float va = lane < n ? sm.cand_v[row][lane] : 0.f;
       const int ka = lane < n ? sm.cand_k[row][lane] : 0;
+      const uint32_t key = lane < n ? ordered_key(va) : 0u;    // > 0 for every candidate (finite scores)
       int rank = 0;
-#pragma unroll 4
-      for (int b = 0; b < n; ++b) {        // n is warp-uniform
-        const float vb = __shfl_sync(0xffffffffu, va, b);
-        const int kb = __shfl_sync(0xffffffffu, ka, b);
-        rank += (vb > va || (vb == va && kb < ka)) ? 1 : 0;
+#pragma unroll 8
+      for (int b = 0; b < n; ++b)            // n is warp-uniform
+        rank += (__shfl_sync(0xffffffffu, key, b) > key) ? 1 : 0;
+      const uint32_t same = __match_any_sync(0xffffffffu, key);
+      if (__any_sync(0xffffffffu, lane < n && (same & (same - 1u)) != 0u)) {
+        for (int b = 0; b < n; ++b) {
+          const uint32_t kb = __shfl_sync(0xffffffffu, key, b);
+          const int pb = __shfl_sync(0xffffffffu, ka, b);
+          rank += (kb == key && pb < ka) ? 1 : 0;
+        }
       }
       const bool keep = lane < n && rank < TOPK;
-      uint32_t m = __ballot_sync(0xffffffffu, keep);
-      n_sel = __popc(m);
-      int pos = 0;                         // ascending page order: kept pages below mine
-      while (m != 0u) {
-        const int src = __ffs(m) - 1;
-        m &= m - 1;
-        pos += (__shfl_sync(0xffffffffu, ka, src) < ka) ? 1 : 0;
+      uint32_t* map = reinterpret_cast<uint32_t*>(sm.cand_v[row]);
+      __syncwarp();
+      map[lane] = 0u;
+      __syncwarp();
+      if (keep) atomicOr(&map[ka >> 5], 1u << (ka & 31));
+      __syncwarp();
+      uint32_t w = map[lane];
+      const int mine = __popc(w);
+      int pre = mine;
+#pragma unroll
+      for (int s2 = 1; s2 < 32; s2 <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, pre, s2);
+        if (lane >= s2) pre += up;
       }
-      if (keep) o[pos] = ka;
+      n_sel = __shfl_sync(0xffffffffu, pre, 31);
+      int pos = pre - mine;
+      while (w != 0u) {
+        const int bit = __ffs(w) - 1;
+        w &= w - 1;
+        o[pos++] = lane * 32 + bit;
+      }
       for (int a = lane; a < TOPK; a += 32)
         if (a >= n_sel) o[a] = -1;
       continue;
