@@ -438,8 +438,15 @@ topk_select_fast_kernel(const __grid_constant__ CUtensorMap tmap_ms, int H, int 
       float v[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) v[e] = col[(i0 + e) * 16 * kFastTok];
+      if constexpr (GPT <= 4) {
+        // v[e] and v[e + GPT] belong to the same group: one three-input max for the two (NaN never wins)
 #pragma unroll
-      for (int e = 0; e < 8; ++e) gm[(i0 + e) % GPT] = fmaxf(gm[(i0 + e) % GPT], v[e]);   // NaN never wins
+        for (int e = 0; e < 8; ++e)
+          if ((e / GPT) % 2 == 0) gm[e % GPT] = max3(gm[e % GPT], v[e], v[e + GPT]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) gm[(i0 + e) % GPT] = fmaxf(gm[(i0 + e) % GPT], v[e]);
+      }
     }
   } else {
     for (int i0 = 0; i0 < 64; i0 += 8) {
@@ -595,45 +602,57 @@ topk_select_fast_kernel(const __grid_constant__ CUtensorMap tmap_ms, int H, int 
     }
     if (n <= 64) {
       // two candidates per lane (slots lane and lane + 32), same method
-      const int n0 = min(n, 32);
-      const float va0 = lane < n ? sm.cand_v[row][lane] : 0.f;
-      const int ka0 = lane < n ? sm.cand_k[row][lane] : 0;
-      const float va1 = lane + 32 < n ? sm.cand_v[row][lane + 32] : 0.f;
-      const int ka1 = lane + 32 < n ? sm.cand_k[row][lane + 32] : 0;
+      const float va0 = sm.cand_v[row][lane], va1 = lane + 32 < n ? sm.cand_v[row][lane + 32] : 0.f;
+      const int ka0 = sm.cand_k[row][lane], ka1 = lane + 32 < n ? sm.cand_k[row][lane + 32] : 0;
+      const uint32_t key0 = ordered_key(va0), key1 = lane + 32 < n ? ordered_key(va1) : 0u;
       int rank0 = 0, rank1 = 0;
-#pragma unroll 4
-      for (int b = 0; b < n0; ++b) {        // n is warp-uniform
-        const float vb = __shfl_sync(0xffffffffu, va0, b);
-        const int kb = __shfl_sync(0xffffffffu, ka0, b);
-        rank0 += (vb > va0 || (vb == va0 && kb < ka0)) ? 1 : 0;
-        rank1 += (vb > va1 || (vb == va1 && kb < ka1)) ? 1 : 0;
+#pragma unroll 8
+      for (int b = 0; b < 32; ++b) {
+        const uint32_t kb = __shfl_sync(0xffffffffu, key0, b);
+        rank0 += (kb > key0) ? 1 : 0;
+        rank1 += (kb > key1) ? 1 : 0;
       }
       for (int b = 32; b < n; ++b) {
-        const float vb = __shfl_sync(0xffffffffu, va1, b - 32);
-        const int kb = __shfl_sync(0xffffffffu, ka1, b - 32);
-        rank0 += (vb > va0 || (vb == va0 && kb < ka0)) ? 1 : 0;
-        rank1 += (vb > va1 || (vb == va1 && kb < ka1)) ? 1 : 0;
+        const uint32_t kb = __shfl_sync(0xffffffffu, key1, b - 32);
+        rank0 += (kb > key0) ? 1 : 0;
+        rank1 += (kb > key1) ? 1 : 0;
       }
-      const bool keep0 = lane < n && rank0 < TOPK, keep1 = lane + 32 < n && rank1 < TOPK;
-      uint32_t m0 = __ballot_sync(0xffffffffu, keep0), m1 = __ballot_sync(0xffffffffu, keep1);
-      n_sel = __popc(m0) + __popc(m1);
-      int pos0 = 0, pos1 = 0;               // ascending page order: kept pages below mine
-      while (m0 != 0u) {
-        const int src = __ffs(m0) - 1;
-        m0 &= m0 - 1;
-        const int kb = __shfl_sync(0xffffffffu, ka0, src);
-        pos0 += (kb < ka0) ? 1 : 0;
-        pos1 += (kb < ka1) ? 1 : 0;
+      // equal scores: ordered by page (the slower exact comparison, only when some score repeats)
+      const uint32_t same0 = __match_any_sync(0xffffffffu, key0), same1 = __match_any_sync(0xffffffffu, key1);
+      bool dup = (same0 & (same0 - 1u)) != 0u || (lane + 32 < n && (same1 & (same1 - 1u)) != 0u);
+      // a score may also repeat across the two slots: compare against every key of the other slot
+      for (int b = 0; b < n - 32; ++b) dup |= __shfl_sync(0xffffffffu, key1, b) == key0;
+      if (__any_sync(0xffffffffu, dup)) {
+        for (int b = 0; b < n; ++b) {
+          const uint32_t kb = b < 32 ? __shfl_sync(0xffffffffu, key0, b) : __shfl_sync(0xffffffffu, key1, b - 32);
+          const int pb = b < 32 ? __shfl_sync(0xffffffffu, ka0, b) : __shfl_sync(0xffffffffu, ka1, b - 32);
+          rank0 += (kb == key0 && pb < ka0) ? 1 : 0;
+          rank1 += (kb == key1 && pb < ka1) ? 1 : 0;
+        }
       }
-      while (m1 != 0u) {
-        const int src = __ffs(m1) - 1;
-        m1 &= m1 - 1;
-        const int kb = __shfl_sync(0xffffffffu, ka1, src);
-        pos0 += (kb < ka0) ? 1 : 0;
-        pos1 += (kb < ka1) ? 1 : 0;
+      const bool keep0 = rank0 < TOPK, keep1 = lane + 32 < n && rank1 < TOPK;
+      uint32_t* map = reinterpret_cast<uint32_t*>(sm.cand_v[row]);
+      __syncwarp();
+      map[lane] = 0u;
+      __syncwarp();
+      if (keep0) atomicOr(&map[ka0 >> 5], 1u << (ka0 & 31));
+      if (keep1) atomicOr(&map[ka1 >> 5], 1u << (ka1 & 31));
+      __syncwarp();
+      uint32_t w = map[lane];
+      const int mine = __popc(w);
+      int pre = mine;
+#pragma unroll
+      for (int s2 = 1; s2 < 32; s2 <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, pre, s2);
+        if (lane >= s2) pre += up;
       }
-      if (keep0) o[pos0] = ka0;
-      if (keep1) o[pos1] = ka1;
+      n_sel = __shfl_sync(0xffffffffu, pre, 31);
+      int pos = pre - mine;
+      while (w != 0u) {
+        const int bit = __ffs(w) - 1;
+        w &= w - 1;
+        o[pos++] = lane * 32 + bit;
+      }
       for (int a = lane; a < TOPK; a += 32)
         if (a >= n_sel) o[a] = -1;
       continue;
