@@ -546,7 +546,81 @@ topk_select_fast_kernel(const __grid_constant__ CUtensorMap tmap_ms, int H, int 
   __syncthreads();
 
   // ---- C: rank, keep, order, emit (warp w: rows 2w, 2w + 1) --------------------------------------------------
-  for (int rr = 0; rr < 2; ++rr) {
+  // Both rows at once when each has at most one candidate per lane (the usual case): the steps below are chains of
+  // shuffles and shared-memory round trips, and two independent chains hide each other's latency.  The method is
+  // the one described at the single-row code that follows (which takes every other case).
+  bool both_done = false;
+  if (t0 + warp * 2 + 1 < T && sm.cnt[warp * 2] <= 32 && sm.cnt[warp * 2 + 1] <= 32) {
+    const int row0 = warp * 2;
+    int nn[2], ka[2], rank[2] = {0, 0};
+    uint32_t key[2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      nn[q] = sm.cnt[row0 + q];
+      const float va = lane < nn[q] ? sm.cand_v[row0 + q][lane] : 0.f;
+      ka[q] = lane < nn[q] ? sm.cand_k[row0 + q][lane] : 0;
+      key[q] = lane < nn[q] ? ordered_key(va) : 0u;
+    }
+    const int nmax = max(nn[0], nn[1]);
+#pragma unroll 8
+    for (int b = 0; b < nmax; ++b) {         // past a row's last candidate the key read is 0 and counts for nothing
+#pragma unroll
+      for (int q = 0; q < 2; ++q) rank[q] += (__shfl_sync(0xffffffffu, key[q], b) > key[q]) ? 1 : 0;
+    }
+    bool dup = false;
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const uint32_t same = __match_any_sync(0xffffffffu, key[q]);
+      dup |= lane < nn[q] && (same & (same - 1u)) != 0u;
+    }
+    if (__any_sync(0xffffffffu, dup)) {
+      for (int b = 0; b < nmax; ++b) {
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const uint32_t kb = __shfl_sync(0xffffffffu, key[q], b);
+          const int pb = __shfl_sync(0xffffffffu, ka[q], b);
+          rank[q] += (kb != 0u && kb == key[q] && pb < ka[q]) ? 1 : 0;
+        }
+      }
+    }
+    uint32_t* map0 = reinterpret_cast<uint32_t*>(sm.cand_v[row0]);
+    uint32_t* map1 = reinterpret_cast<uint32_t*>(sm.cand_v[row0 + 1]);
+    __syncwarp();
+    map0[lane] = 0u;
+    map1[lane] = 0u;
+    __syncwarp();
+    if (lane < nn[0] && rank[0] < TOPK) atomicOr(&map0[ka[0] >> 5], 1u << (ka[0] & 31));
+    if (lane < nn[1] && rank[1] < TOPK) atomicOr(&map1[ka[1] >> 5], 1u << (ka[1] & 31));
+    __syncwarp();
+    uint32_t w[2] = {map0[lane], map1[lane]};
+    int mine[2], pre[2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) pre[q] = mine[q] = __popc(w[q]);
+#pragma unroll
+    for (int s2 = 1; s2 < 32; s2 <<= 1) {
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int up = __shfl_up_sync(0xffffffffu, pre[q], s2);
+        if (lane >= s2) pre[q] += up;
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      int* o = out + (static_cast<size_t>(t0 + row0 + q) * H + h) * TOPK;
+      const int n_sel = __shfl_sync(0xffffffffu, pre[q], 31);
+      int pos = pre[q] - mine[q];
+      uint32_t ww = w[q];
+      while (ww != 0u) {
+        const int bit = __ffs(ww) - 1;
+        ww &= ww - 1;
+        o[pos++] = lane * 32 + bit;
+      }
+      for (int a = lane; a < TOPK; a += 32)
+        if (a >= n_sel) o[a] = -1;
+    }
+    both_done = true;
+  }
+  for (int rr = 0; rr < 2 && !both_done; ++rr) {
     const int row = warp * 2 + rr;
     const int tok = t0 + row;
     if (tok >= T) continue;                // warp-uniform
