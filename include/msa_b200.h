@@ -131,6 +131,13 @@ int msa_topk_select(const float* max_score, int32_t num_heads, int32_t max_k_til
 int msa_block_max(const float* max_score, int32_t num_heads, int32_t max_k_tiles, int32_t total_q,
                   const int32_t* block_starts, int32_t n_blocks, float* out, void* stream);
 
+/* The other end of the per-block granularity: `block_lists` int32 [n_blocks, num_heads, topk] (what
+ * msa_topk_select returns on the output of msa_block_max) is written to every token of its block,
+ * out int32 [total_q, num_heads, topk] -- the per-token layout `kv_block_indexes` has in the reference
+ * (python/fmha_sm100/api.py:1046-1060).  num_heads * topk must be a multiple of 4, both buffers 16-byte aligned. */
+int msa_expand_block_lists(const int32_t* block_lists, const int32_t* block_starts, int32_t n_blocks,
+                           int32_t num_heads, int32_t topk, int32_t* out, void* stream);
+
 /* ---------------------------------------------------------------------------
  * Stages 1 and 3 (prefill): dense / score-only / block-sparse paged attention.
  * Replaces the TVM-FFI function `run_<variant>(...34 args...)`

@@ -167,6 +167,8 @@ def _bind(lib):
     lib.msa_topk_select.argtypes = [vp, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, vp, vp]
     lib.msa_block_max.restype = c_int32
     lib.msa_block_max.argtypes = [vp, c_int32, c_int32, c_int32, vp, c_int32, vp, vp]
+    lib.msa_expand_block_lists.restype = c_int32
+    lib.msa_expand_block_lists.argtypes = [vp, vp, c_int32, c_int32, c_int32, vp, vp]
     lib.msa_fmha_combine.restype = c_int32
     lib.msa_fmha_combine.argtypes = [vp, vp, c_int32, c_int64, c_int32, vp, vp, vp]
     lib.msa_fp4_dequant_rows.restype = c_int32

@@ -730,10 +730,8 @@ def sparse_topk_select(
     sel = torch.empty(nblk, H, topk, dtype=torch.int32, device=dev)
     check(lib.msa_topk_select(_ptr(bm), H, K, nblk, topk, nvp, int(force_begin_blocks), int(force_end_blocks),
                               _ptr(sel), _stream()), "msa_topk_select")
-    owner = torch.repeat_interleave(torch.arange(nblk, device=dev), (starts[1:] - starts[:-1]).long(),
-                                    output_size=T)
-    res = sel.index_select(0, owner)
-    if output is not None:
-        output.copy_(res)
-        return output
-    return res
+    out = output if output is not None else torch.empty(T, H, topk, dtype=torch.int32, device=dev)
+    assert out.is_contiguous() and out.dtype == torch.int32 and tuple(out.shape) == (T, H, topk)
+    check(lib.msa_expand_block_lists(_ptr(sel), _ptr(starts), nblk, H, topk, _ptr(out), _stream()),
+          "msa_expand_block_lists")
+    return out

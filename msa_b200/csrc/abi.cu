@@ -68,6 +68,12 @@ int msa_block_max(const float* max_score, int32_t num_heads, int32_t max_k_tiles
                         static_cast<cudaStream_t>(stream));
 }
 
+int msa_expand_block_lists(const int32_t* block_lists, const int32_t* block_starts, int32_t n_blocks,
+                           int32_t num_heads, int32_t topk, int32_t* out, void* stream) {
+  return msa::expand_block_lists(block_lists, block_starts, n_blocks, num_heads, topk, out,
+                                 static_cast<cudaStream_t>(stream));
+}
+
 int msa_fp4_dequant_rows(const void* packed, const void* scales, int32_t format, int32_t scale_layout, int64_t rows,
                          int32_t heads, void* out, void* stream) {
   return msa::fp4_dequant_rows(packed, scales, format, scale_layout, rows, heads, out,

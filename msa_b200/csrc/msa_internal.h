@@ -45,6 +45,8 @@ class DeviceSetup {
 int topk_select(const float* ms, int H, int K, int T, int topk, int nvp, int fb, int fe, int* out, cudaStream_t st);
 int block_max(const float* ms, int H, int K, int T, const int* block_starts, int n_blocks, float* out,
               cudaStream_t st);
+int expand_block_lists(const int* lists, const int* block_starts, int n_blocks, int H, int topk, int* out,
+                       cudaStream_t st);
 int fmha_fwd(const msa_fmha_args* a, cudaStream_t st);
 void set_timing_buffer(void* ptr);
 int fmha_combine(const void* partial_out, const float* partial_lse, int n_splits, int64_t total_q, int num_qo_heads,

@@ -947,4 +947,28 @@ int block_max(const float* ms, int H, int K, int T, const int* block_starts, int
   return static_cast<int>(cudaGetLastError());
 }
 
+// [n_blocks, row] -> [T, row]: every token of block b receives the block's row (row = heads x topk page ids,
+// a multiple of four ints).  One CTA per block; 16-byte stores.
+__global__ void __launch_bounds__(256) expand_block_lists_kernel(const int4* __restrict__ lists,
+                                                                const int* __restrict__ block_starts, int row4,
+                                                                int4* __restrict__ out) {
+  const int b = blockIdx.x;
+  const int t0 = block_starts[b], t1 = block_starts[b + 1];
+  const int n = (t1 - t0) * row4;
+  const int4* src = lists + static_cast<size_t>(b) * row4;
+  int4* dst = out + static_cast<size_t>(t0) * row4;
+  for (int i = threadIdx.x; i < n; i += 256) dst[i] = __ldg(src + i % row4);
+}
+
+int expand_block_lists(const int* lists, const int* block_starts, int n_blocks, int H, int topk, int* out,
+                       cudaStream_t st) {
+  if (lists == nullptr || block_starts == nullptr || out == nullptr || H <= 0 || topk <= 0) return MSA_ERR_INVALID;
+  if ((static_cast<long long>(H) * topk) % 4 != 0) return MSA_ERR_UNSUPPORTED;
+  if (((reinterpret_cast<uintptr_t>(lists) | reinterpret_cast<uintptr_t>(out)) & 15) != 0) return MSA_ERR_INVALID;
+  if (n_blocks <= 0) return MSA_OK;
+  expand_block_lists_kernel<<<n_blocks, 256, 0, st>>>(reinterpret_cast<const int4*>(lists), block_starts,
+                                                     H * topk / 4, reinterpret_cast<int4*>(out));
+  return static_cast<int>(cudaGetLastError());
+}
+
 }  // namespace msa

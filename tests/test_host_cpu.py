@@ -21,7 +21,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def test_library_exports_every_declared_symbol():
     hdr = open(os.path.join(ROOT, "include", "msa_b200.h")).read()
     names = set(re.findall(r"\b(msa_[a-z0-9_]+)\s*\(", hdr))
-    assert {"msa_topk_select", "msa_fmha_fwd", "msa_decode_fwd", "msa_block_max"} <= names
+    assert {"msa_topk_select", "msa_fmha_fwd", "msa_decode_fwd", "msa_block_max", "msa_expand_block_lists"} <= names
     lib = msa_b200.get_lib()
     for n in sorted(names):
         assert hasattr(lib, n), f"{n} declared in the header but not exported"
