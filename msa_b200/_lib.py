@@ -20,6 +20,8 @@ CSRC = os.path.join(_HERE, "csrc")
 SOURCES = ["abi.cu", "topk.cu", "decode.cu", "fmha_host.cu", "kv_quant.cu", "plan_host.cu", "csr.cu", "fp4_indexer.cu"]
 
 MSA_KV_BF16, MSA_KV_FP8_E4M3, MSA_KV_NVFP4 = 0, 1, 2
+MSA_ERR_INVALID = -1
+MSA_ERR_UNSUPPORTED = -2
 MSA_ERR_TIMEOUT = -3
 MSA_ERR_BOUNDS = -6
 ABI_VERSION = 4

@@ -42,6 +42,26 @@ def test_argument_validation_without_gpu():
     assert lib.msa_decode_fwd(None, None) == -1
     assert lib.msa_decode_workspace_bytes(32, 64, 8) == 32 * 64 * 8 * 130 * 4
     assert lib.msa_decode_workspace_bytes(32, 64, 1) == 0
+    # block lists -> per-token lists: null pointers, a row that is not a multiple of four ints, unaligned buffers
+    assert lib.msa_expand_block_lists(None, None, 1, 1, 16, None, None) == _lib.MSA_ERR_INVALID
+    assert lib.msa_expand_block_lists(256, 512, 1, 1, 3, 1024, None) == _lib.MSA_ERR_UNSUPPORTED
+    assert lib.msa_expand_block_lists(260, 512, 1, 1, 16, 1024, None) == _lib.MSA_ERR_INVALID
+    assert lib.msa_expand_block_lists(256, 512, 0, 1, 16, 1024, None) == 0      # no blocks: nothing to do
+
+
+def test_fp8_pv_precision_setting():
+    """The module-level choice behind msa_fmha_args.fp8_p_f16: two modes, restored by the context manager."""
+    assert msa_b200.get_fp8_pv_precision() == "e4m3"
+    with msa_b200.fp8_pv_precision("f16"):
+        assert msa_b200.get_fp8_pv_precision() == "f16"
+        with msa_b200.fp8_pv_precision("e4m3"):
+            assert msa_b200.get_fp8_pv_precision() == "e4m3"
+        assert msa_b200.get_fp8_pv_precision() == "f16"
+    assert msa_b200.get_fp8_pv_precision() == "e4m3"
+    assert msa_b200.set_fp8_pv_precision("f16") == "e4m3" and msa_b200.set_fp8_pv_precision("e4m3") == "f16"
+    with pytest.raises(ValueError):
+        msa_b200.set_fp8_pv_precision("bf16")
+    assert "fp8_p_f16" in [f[0] for f in _lib.FmhaArgs._fields_]
 
 
 def test_no_cpu_fallback():
