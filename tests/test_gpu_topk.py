@@ -109,6 +109,20 @@ def test_topk_block_granularity():
         assert torch.equal(got[starts[i]:starts[i + 1]], ref[i:i + 1].expand(starts[i + 1] - starts[i], 2, 16))
 
 
+def test_topk_block_granularity_into_a_given_buffer():
+    """Same through `output=`: msa_expand_block_lists writes the caller's [T, H, topk] tensor, every row of it."""
+    torch.manual_seed(2)
+    starts = [0, 1, 129, 257, 300]
+    ms = torch.randn(3, 128, 300)
+    out = torch.full((300, 3, 32), -7, dtype=torch.int32, device="cuda")
+    got = msa_b200.sparse_topk_select(ms.cuda(), 32, 100, output=out,
+                                      q_block_starts=torch.tensor(starts, dtype=torch.int32))
+    assert got.data_ptr() == out.data_ptr()
+    ref = O.topk_select(O.block_max_score(ms, starts), 32, 100)
+    for i in range(4):
+        assert torch.equal(out[starts[i]:starts[i + 1]].cpu(), ref[i:i + 1].expand(starts[i + 1] - starts[i], 3, 32))
+
+
 def test_topk_large_multiset_property():
     """Full prefill-sized head slice: the selected scores equal torch.topk's as a multiset
     (the check of tests/integration/test_proxy_kv_e2e.py:77-116 of the reference) and rows ascend."""
